@@ -93,28 +93,6 @@ def ncu_md() -> None:
         st = sorted(((float(r[h.index(c)] or 0), c.replace("smsp__pcsamp_warps_issue_stalled_", "")) for c in stall_cols), reverse=True)
         total = sum(v for v, _ in st) or 1.0
         out.append("| warp stall samples | " + ", ".join(f"{n} {100 * v / total:.0f} %" for v, n in st[:6]) + " |")
-    # SASS evidence from the shipped library
-    lib = ROOT / "tiny-llm_b200" / "extensions_b200" / "tiny_llm_ext_b200" / "libtiny_llm_b200.so"
-    sass = subprocess.run(["cuobjdump", "-sass", str(lib)], capture_output=True, text=True).stdout
-    out.append("\n## SASS evidence (`cuobjdump -sass libtiny_llm_b200.so`, mnemonic counts per kernel)\n\n| kernel | UTCHMMA (tcgen05.mma) | of which `.2CTA` | UTCBAR (commit) | LDTM / STTM (tcgen05.ld / st) | UTMALDG (TMA) |\n|---|---|---|---|---|---|")
-    cur, counts = None, collections.OrderedDict()
-    for line in sass.splitlines():
-        m = re.search(r"Function : (\S+)", line)
-        if m:
-            cur = m.group(1)
-            counts[cur] = collections.Counter()
-            continue
-        if cur:
-            for mn in ("UTCHMMA", "UTCBAR", "LDTM", "STTM", "UTMALDG"):
-                if mn in line:
-                    counts[cur][mn] += 1
-            if "UTCHMMA.2CTA" in line:
-                counts[cur]["2CTA"] += 1
-    demangle = subprocess.run(["c++filt"], input="\n".join(counts), capture_output=True, text=True).stdout.splitlines()
-    for name, c in zip(demangle, counts.values()):
-        if c["UTCHMMA"] or c["UTMALDG"]:
-            short = name.split("(")[0].replace("void ", "").replace("tl::", "")[:80]
-            out.append(f"| `{short}` | {c['UTCHMMA']} | {c['2CTA']} | {c['UTCBAR']} | {c['LDTM']} / {c['STTM']} | {c['UTMALDG']} |")
     (PROF / "r02_ncu_kernels.md").write_text("\n".join(out) + "\n")
 
 
