@@ -1,0 +1,101 @@
+/*
+ * tiny_llm_b200_blocks.h - C ABI of libtiny_llm_b200_blocks.so: building blocks for decoder layers with
+ * unquantised (bf16 or fp32) weights on B200 (sm_100a): row-wise norms with a residual stream kept in fp32,
+ * rotary positions in both pair layouts, paged latent (low-rank) key/value storage, latent attention with an
+ * optional sliding window over ragged batches, gated activations and a top-k mixture-of-experts feed-forward.
+ *
+ * Conventions are those of tiny_llm_b200.h: plain device pointers and sizes, the caller owns every buffer, a
+ * launcher never allocates, frees or synchronises and enqueues on `stream` (a cudaStream_t passed as void*);
+ * 0 on success, a negative TL_E* code otherwise with the text in tlb_last_error().  `dtype` (TL_F32 | TL_BF16)
+ * names the storage type of activations, weights and the cache; sums, norms, softmax, router logits and the
+ * residual stream are fp32 in both.
+ *
+ * A ragged batch is a flat list of T tokens; token t belongs to sequence row tok_seq[t] of the step's block
+ * table and sits at position tok_pos[t] of that sequence.
+ */
+#ifndef TINY_LLM_B200_BLOCKS_H
+#define TINY_LLM_B200_BLOCKS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "tiny_llm_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int tlb_abi_version(void);
+const char *tlb_last_error(void);
+long long tlb_launch_count(void);
+
+/* x32[t,:] = table[ids[t],:] (fp32 residual stream) and h[t,:] = the same row in `dtype`. */
+int tlb_embed_rows(const int32_t *ids, const void *table, float *x32, void *h, int tokens, int vocab, int dim, int dtype,
+                   void *stream);
+
+/* Row-wise RMS norm with optional layer scale and residual accumulation:
+ *   n = y / sqrt(mean(y^2) + eps) * (w + weight_offset)          (* scale, if scale != NULL)
+ *   residual != NULL: residual += n (fp32, in place), h = residual rounded to `dtype` (if h != NULL)
+ *   residual == NULL: h = n rounded to `dtype`.
+ * y is fp32 when y_is_f32, else `dtype`; w and scale are `dtype`. */
+int tlb_norm_residual(const void *y, int y_is_f32, const void *w, float weight_offset, const void *scale, float eps, float *residual,
+                      void *h, int rows, int dim, int dtype, void *stream);
+
+/* Rotary positions, in place, on `dims` entries starting at `first` within every head of x [rows, heads] (strides in
+ * elements).  interleaved = 0: pair (i, i + dims/2); 1: pair (2i, 2i+1).  angle = tok_pos[row] * base^(-2i/dims). */
+int tlb_rope_rows(void *x, long long row_stride, long long head_stride, int first, int heads, int dims, int interleaved, double base,
+                  const int32_t *tok_pos, int rows, int dtype, void *stream);
+
+/* Latent cache append: for every token, the first `rank` entries of down[t,:] are RMS-normed (plain weight) and the last
+ * `rot` entries rotated by the token's position; both are stored at the token's slot of slab [pages, page_size, rank+rot]
+ * found through block_table [*, max_pages] (row tok_seq[t], page tok_pos[t] / page_size). */
+int tlb_latent_append(const void *down, const void *norm_w, float eps, int rank, int rot, int rot_dims, int interleaved, double base,
+                      const int32_t *tok_pos, const int32_t *tok_seq, const int32_t *block_table, int max_pages, int num_pages,
+                      int page_size, void *slab, int tokens, int dtype, void *stream);
+
+/* Latent (absorbed multi-query) attention over the paged latent cache.  Query row (t, h) is the concatenation of
+ * q_lat[t,h,0:rank] and q_rot[t,h,0:rot] (two pointers with token / head strides in elements); key j of the token's
+ * sequence is slab row j (rank + rot entries), value j its first `rank` entries.  Token t sees keys j <= tok_pos[t] and,
+ * with window > 0, tok_pos[t] - j < window.  out[t,h,0:rank] = softmax(scale * q.k) . values.
+ * tiles [num_tiles, 3] int32: first flat token, token count (1..TLB_ATTENTION_TILE_TOKENS, consecutive positions of one
+ * sequence), block-table row. */
+#define TLB_ATTENTION_TILE_TOKENS 4
+int tlb_latent_attention(const void *q_lat, long long ql_token, long long ql_head, const void *q_rot, long long qr_token,
+                         long long qr_head, const void *slab, int num_pages, int page_size, int rank, int rot,
+                         const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles, const int32_t *tok_pos,
+                         int heads, int window, float scale, void *out, long long o_token, long long o_head, int dtype, void *stream);
+
+/* out[t, j] = act(gu[t, j]) * gu[t, width + j]; act 0 = silu, 1 = gelu (tanh form). */
+int tlb_gated_act(const void *gu, void *out, int rows, int width, int act, int dtype, void *stream);
+
+/* Router: logits = W h + b in fp32 (h, W, b stored in `dtype`), the `top` largest per token (lower index wins a tie),
+ * weights = softmax over the chosen logits.  idx [tokens, top] int32, gate [tokens, top] fp32. */
+int tlb_moe_route(const void *h, const void *w, const void *b, int tokens, int dim, int experts, int top, int32_t *idx, float *gate,
+                  int dtype, void *stream);
+
+/* Rows per expert tile of the grouped products, and the sizes a caller has to provide. */
+#define TLB_MOE_TILE_ROWS 32
+/* upper bound of sorted rows (pairs grouped by expert, every group padded to whole tiles) */
+long long tlb_moe_max_rows(int tokens, int top, int experts);
+/* Group the (token, choice) pairs by expert: sorted_pair [max_rows] (pair id or -1), tile_expert [max_rows / TILE],
+ * counters [2] = {tiles in use, rows in use}.  One launch, no host involvement. */
+int tlb_moe_sort(const int32_t *idx, int tokens, int top, int experts, int32_t *sorted_pair, int32_t *tile_expert, int32_t *counters,
+                 void *stream);
+/* inter[row, :] = act(Wg[e] h[token(row)]) * (Wu[e] h[token(row)]); Wg, Wu [experts, ff, dim]; inter [max_rows, ff]. */
+int tlb_moe_gate_up(const void *h, const void *wg, const void *wu, const int32_t *sorted_pair, const int32_t *tile_expert,
+                    const int32_t *counters, int tokens, int top, int experts, int dim, int ff, int act, void *inter, int dtype,
+                    void *stream);
+/* pair_out[pair, :] = Wd[e] inter[row, :] (fp32); Wd [experts, dim, ff]. */
+int tlb_moe_down(const void *inter, const void *wd, const int32_t *sorted_pair, const int32_t *tile_expert, const int32_t *counters,
+                 int tokens, int top, int experts, int dim, int ff, float *pair_out, int dtype, void *stream);
+/* y[t,:] = sum_k gate[t,k] * pair_out[t*top+k,:] (+ shared[t,:] if shared != NULL, stored in `dtype`), fp32, in choice order. */
+int tlb_moe_combine(const float *pair_out, const float *gate, const void *shared, float *y, int tokens, int top, int dim, int dtype,
+                    void *stream);
+
+/* Row-wise arg-max of fp32 logits [rows, vocab] (lowest index wins a tie). */
+int tlb_argmax_rows(const float *logits, int32_t *out, int rows, int vocab, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

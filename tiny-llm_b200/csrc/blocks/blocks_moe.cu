@@ -1,0 +1,261 @@
+// Top-k mixture-of-experts feed-forward: router (fp32 logits, top-k, softmax over the chosen), grouping of the
+// (token, choice) pairs by expert on the device, the two grouped products and the weighted combination.
+//
+// The pairs of one expert occupy whole 32-row tiles of a sorted row list, so every CTA of the grouped products reads
+// ONE expert's weights; rows are gathered from / scattered to token order through the list.  Each output row is a sum
+// over the reduction index in a fixed order and the combination adds a token's choices in choice order, so a token's
+// result does not depend on which other tokens are in the batch.
+#include "blocks_common.cuh"
+
+namespace tlb {
+
+constexpr int kTileRows = TLB_MOE_TILE_ROWS;
+
+__device__ __forceinline__ float moe_act(float z, int act) {
+    if (act == 0) return z / (1.0f + expf(-z));
+    float inner = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+    return 0.5f * z * (1.0f + tanhf(inner));
+}
+
+// One warp per token.  Logits live in shared memory [warps][experts].
+template <typename T>
+__global__ void moe_route_kernel(const T *__restrict__ h, const T *__restrict__ w, const T *__restrict__ b, int tokens, int dim, int experts,
+                                 int top, int32_t *__restrict__ idx, float *__restrict__ gate) {
+    extern __shared__ float logits[];
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= tokens) return;
+    float *z = logits + warp * experts;
+    const T *x = h + (size_t)t * dim;
+    for (int e = 0; e < experts; ++e) {
+        const T *row = w + (size_t)e * dim;
+        float s = 0.f;
+        for (int d = lane; d < dim; d += 32) s = fmaf(to_f(x[d]), to_f(row[d]), s);
+        s = warp_sum(s);
+        if (lane == 0) z[e] = s + (b ? to_f(b[e]) : 0.f);
+    }
+    __syncwarp();
+    // top-k by repeated arg-max over the warp (lower index wins a tie)
+    float chosen_v = 0.f, first_v = 0.f, denom = 0.f;
+    int chosen_i = 0;
+    for (int k = 0; k < top; ++k) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            float v = z[e];
+            if (v > bv || (v == bv && e < bi)) bv = v, bi = e;
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+        }
+        if (k == 0) first_v = bv;
+        float p = expf(bv - first_v);  // the first choice is the largest logit
+        denom += p;
+        if (lane == k % 32 && k < 32) chosen_v = p, chosen_i = bi;
+        if (k >= 32 && lane == 0) {  // more than 32 choices: write straight through, normalised below
+            idx[(size_t)t * top + k] = bi;
+            gate[(size_t)t * top + k] = p;
+        }
+        __syncwarp();
+        if (lane == 0 && bi != 0x7fffffff) z[bi] = -INFINITY;
+        __syncwarp();
+    }
+    if (lane < top && lane < 32) {
+        idx[(size_t)t * top + lane] = chosen_i;
+        gate[(size_t)t * top + lane] = chosen_v / denom;
+    }
+    if (top > 32 && lane == 0)
+        for (int k = 32; k < top; ++k) gate[(size_t)t * top + k] /= denom;
+}
+
+// Single CTA: histogram, padded exclusive scan, scatter.
+__global__ void moe_sort_kernel(const int32_t *__restrict__ idx, int pairs, int experts, int max_rows, int32_t *__restrict__ sorted_pair,
+                                int32_t *__restrict__ tile_expert, int32_t *__restrict__ counters) {
+    extern __shared__ int sm[];
+    int *count = sm, *start = sm + experts, *cursor = sm + 2 * experts;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0, cursor[e] = 0;
+    for (int r = threadIdx.x; r < max_rows; r += blockDim.x) sorted_pair[r] = -1;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        int e = idx[p];
+        if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int row = 0;
+        for (int e = 0; e < experts; ++e) {
+            start[e] = row;
+            int tiles = (count[e] + kTileRows - 1) / kTileRows;
+            for (int i = 0; i < tiles; ++i) tile_expert[row / kTileRows + i] = e;
+            row += tiles * kTileRows;
+        }
+        counters[0] = row / kTileRows;
+        counters[1] = row;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        int e = idx[p];
+        if (e >= 0 && e < experts) sorted_pair[start[e] + atomicAdd(&cursor[e], 1)] = p;
+    }
+}
+
+// C tile [32 rows x 64 columns] of  A[rows, K] . W[e][cols, K]^T, fp32 accumulation in k order.
+// 256 threads: thread (ty, tx) owns rows 2 ty .. 2 ty + 1 and columns tx + 16 c, c = 0..3.
+constexpr int kBN = 64, kBK = 16;
+
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_grouped_kernel(const T *__restrict__ a, const T *__restrict__ w1, const T *__restrict__ w2, const int32_t *__restrict__ sorted_pair,
+                   const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ counters, int top, int K, int N, int act,
+                   T *__restrict__ inter, float *__restrict__ pair_out) {
+    if ((int)blockIdx.x >= counters[0]) return;
+    __shared__ float sa[kBK][kTileRows + 1];
+    __shared__ float sb1[kBK][kBN + 1];
+    __shared__ float sb2[GATED ? kBK : 1][kBN + 1];
+    __shared__ int src_row[kTileRows];
+    const int e = tile_expert[blockIdx.x];
+    const int row0 = blockIdx.x * kTileRows, col0 = blockIdx.y * kBN;
+    if (threadIdx.x < kTileRows) {
+        int pair = sorted_pair[row0 + threadIdx.x];
+        // gate/up gather token rows of h; the down product reads the sorted intermediate rows
+        src_row[threadIdx.x] = pair < 0 ? -1 : (GATED ? pair / top : row0 + (int)threadIdx.x);
+    }
+    __syncthreads();
+    const T *wa = w1 + (size_t)e * N * K;
+    const T *wb = GATED ? w2 + (size_t)e * N * K : nullptr;
+    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
+    float c1[2][4] = {}, c2[2][4] = {};
+    for (int k0 = 0; k0 < K; k0 += kBK) {
+        for (int i = threadIdx.x; i < kTileRows * kBK; i += 256) {
+            int r = i / kBK, k = i % kBK;
+            int sr = src_row[r];
+            sa[k][r] = (sr >= 0 && k0 + k < K) ? to_f(a[(size_t)sr * K + k0 + k]) : 0.f;
+        }
+        for (int i = threadIdx.x; i < kBN * kBK; i += 256) {
+            int n = i / kBK, k = i % kBK;
+            bool ok = col0 + n < N && k0 + k < K;
+            sb1[k][n] = ok ? to_f(wa[(size_t)(col0 + n) * K + k0 + k]) : 0.f;
+            if (GATED) sb2[k][n] = ok ? to_f(wb[(size_t)(col0 + n) * K + k0 + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < kBK; ++k) {
+            float a0 = sa[k][2 * ty], a1 = sa[k][2 * ty + 1];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float b = sb1[k][tx + 16 * c];
+                c1[0][c] = fmaf(a0, b, c1[0][c]);
+                c1[1][c] = fmaf(a1, b, c1[1][c]);
+                if (GATED) {
+                    float b2 = sb2[k][tx + 16 * c];
+                    c2[0][c] = fmaf(a0, b2, c2[0][c]);
+                    c2[1][c] = fmaf(a1, b2, c2[1][c]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        int row = row0 + 2 * ty + r;
+        int pair = sorted_pair[row];
+        if (pair < 0) continue;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            int col = col0 + tx + 16 * c;
+            if (col >= N) continue;
+            if (GATED) inter[(size_t)row * N + col] = from_f<T>(moe_act(c1[r][c], act) * c2[r][c]);
+            else pair_out[(size_t)pair * N + col] = c1[r][c];
+        }
+    }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const float *__restrict__ pair_out, const float *__restrict__ gate, const T *__restrict__ shared,
+                                   float *__restrict__ y, int top, int dim) {
+    int t = blockIdx.x;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < top; ++k) s = fmaf(gate[(size_t)t * top + k], pair_out[((size_t)t * top + k) * dim + d], s);
+        if (shared) s += to_f(shared[(size_t)t * dim + d]);
+        y[(size_t)t * dim + d] = s;
+    }
+}
+
+}  // namespace tlb
+
+using namespace tlb;
+
+extern "C" {
+
+int tlb_moe_route(const void *h, const void *w, const void *b, int tokens, int dim, int experts, int top, int32_t *idx, float *gate, int dtype,
+                  void *stream) {
+    if (tokens <= 0) return TL_OK;
+    if (!h || !w || !idx || !gate || dim <= 0 || experts <= 0 || top <= 0 || top > experts) return tl::fail(TL_EINVAL, "moe_route: bad argument");
+    const int warps = 4;
+    size_t smem = (size_t)warps * experts * sizeof(float);
+    if (smem > 48 * 1024) return tl::fail(TL_EINVAL, "moe_route: %d experts do not fit", experts);
+    TLB_DISPATCH(dtype, "moe_route",
+                 moe_route_kernel<T><<<ceil_div(tokens, warps), warps * 32, smem, as_stream(stream)>>>((const T *)h, (const T *)w, (const T *)b, tokens,
+                                                                                                      dim, experts, top, idx, gate));
+    TL_LAUNCH_CHECK("moe_route");
+    return TL_OK;
+}
+
+long long tlb_moe_max_rows(int tokens, int top, int experts) {
+    long long pairs = (long long)tokens * top;
+    long long groups = pairs < experts ? pairs : experts;  // at most min(pairs, experts) groups carry padding
+    long long rows = pairs + groups * (kTileRows - 1);
+    return (rows + kTileRows - 1) / kTileRows * kTileRows;
+}
+
+int tlb_moe_sort(const int32_t *idx, int tokens, int top, int experts, int32_t *sorted_pair, int32_t *tile_expert, int32_t *counters,
+                 void *stream) {
+    if (tokens <= 0) return TL_OK;
+    if (!idx || !sorted_pair || !tile_expert || !counters || top <= 0 || experts <= 0) return tl::fail(TL_EINVAL, "moe_sort: bad argument");
+    size_t smem = (size_t)3 * experts * sizeof(int);
+    if (smem > 48 * 1024) return tl::fail(TL_EINVAL, "moe_sort: %d experts do not fit", experts);
+    moe_sort_kernel<<<1, 1024, smem, as_stream(stream)>>>(idx, tokens * top, experts, (int)tlb_moe_max_rows(tokens, top, experts), sorted_pair,
+                                                          tile_expert, counters);
+    TL_LAUNCH_CHECK("moe_sort");
+    return TL_OK;
+}
+
+int tlb_moe_gate_up(const void *h, const void *wg, const void *wu, const int32_t *sorted_pair, const int32_t *tile_expert, const int32_t *counters,
+                    int tokens, int top, int experts, int dim, int ff, int act, void *inter, int dtype, void *stream) {
+    if (tokens <= 0) return TL_OK;
+    if (!h || !wg || !wu || !sorted_pair || !tile_expert || !counters || !inter || dim <= 0 || ff <= 0 || top <= 0)
+        return tl::fail(TL_EINVAL, "moe_gate_up: bad argument");
+    dim3 grid((unsigned)(tlb_moe_max_rows(tokens, top, experts) / kTileRows), ceil_div(ff, kBN));
+    TLB_DISPATCH(dtype, "moe_gate_up",
+                 moe_grouped_kernel<T, true><<<grid, 256, 0, as_stream(stream)>>>((const T *)h, (const T *)wg, (const T *)wu, sorted_pair, tile_expert,
+                                                                                 counters, top, dim, ff, act, (T *)inter, nullptr));
+    TL_LAUNCH_CHECK("moe_gate_up");
+    return TL_OK;
+}
+
+int tlb_moe_down(const void *inter, const void *wd, const int32_t *sorted_pair, const int32_t *tile_expert, const int32_t *counters, int tokens,
+                 int top, int experts, int dim, int ff, float *pair_out, int dtype, void *stream) {
+    if (tokens <= 0) return TL_OK;
+    if (!inter || !wd || !sorted_pair || !tile_expert || !counters || !pair_out || dim <= 0 || ff <= 0 || top <= 0)
+        return tl::fail(TL_EINVAL, "moe_down: bad argument");
+    dim3 grid((unsigned)(tlb_moe_max_rows(tokens, top, experts) / kTileRows), ceil_div(dim, kBN));
+    TLB_DISPATCH(dtype, "moe_down",
+                 moe_grouped_kernel<T, false><<<grid, 256, 0, as_stream(stream)>>>((const T *)inter, (const T *)wd, nullptr, sorted_pair, tile_expert,
+                                                                                  counters, top, ff, dim, 0, nullptr, pair_out));
+    TL_LAUNCH_CHECK("moe_down");
+    return TL_OK;
+}
+
+int tlb_moe_combine(const float *pair_out, const float *gate, const void *shared, float *y, int tokens, int top, int dim, int dtype, void *stream) {
+    if (tokens <= 0) return TL_OK;
+    if (!pair_out || !gate || !y || top <= 0 || dim <= 0) return tl::fail(TL_EINVAL, "moe_combine: bad argument");
+    TLB_DISPATCH(dtype, "moe_combine",
+                 moe_combine_kernel<T><<<tokens, 256, 0, as_stream(stream)>>>(pair_out, gate, (const T *)shared, y, top, dim));
+    TL_LAUNCH_CHECK("moe_combine");
+    return TL_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,247 @@
+// Row-wise kernels of the blocks library: embedding rows, RMS norm + layer scale + fp32 residual, rotary
+// positions, latent cache append, gated activations, arg-max; and the library's error / launch bookkeeping.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include <atomic>
+
+#include "blocks_common.cuh"
+
+namespace tl {
+// The helpers common.cuh declares; this library is linked on its own.
+static thread_local char g_error[512] = "";
+static std::atomic<long long> g_launches{0};
+int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+int check_launch(const char *what) {
+    cudaError_t e = cudaPeekAtLastError();
+    if (e == cudaSuccess) return TL_OK;
+    cudaGetLastError();
+    return fail(TL_ECUDA, "%s: kernel launch failed: %s", what, cudaGetErrorString(e));
+}
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+bool use_pdl() { return false; }
+}  // namespace tl
+
+namespace tlb {
+
+template <typename T>
+__global__ void embed_rows_kernel(const int32_t *__restrict__ ids, const T *__restrict__ table, float *__restrict__ x32, T *__restrict__ h,
+                                  int vocab, int dim) {
+    int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= vocab) id = 0;
+    const T *row = table + (size_t)id * dim;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        T v = row[d];
+        x32[(size_t)t * dim + d] = to_f(v);
+        if (h) h[(size_t)t * dim + d] = v;
+    }
+}
+
+template <typename T, typename TY>
+__global__ void norm_residual_kernel(const TY *__restrict__ y, const T *__restrict__ w, float weight_offset, const T *__restrict__ scale,
+                                     float eps, float *__restrict__ residual, T *__restrict__ h, int dim) {
+    __shared__ float scratch[33];
+    size_t base = (size_t)blockIdx.x * dim;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float v = to_f(y[base + d]);
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float n = to_f(y[base + d]) * inv * (to_f(w[d]) + weight_offset);
+        if (scale) n *= to_f(scale[d]);
+        if (residual) {
+            n += residual[base + d];
+            residual[base + d] = n;
+        }
+        if (h) h[base + d] = from_f<T>(n);
+    }
+}
+
+template <typename T>
+__global__ void rope_rows_kernel(T *x, long long row_stride, long long head_stride, int first, int heads, int dims, int interleaved,
+                                 double log2_base, const int32_t *__restrict__ tok_pos) {
+    int row = blockIdx.x;
+    int pos = tok_pos[row];
+    int half = dims / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float c, s;
+        rope_angle(pos, i, dims, log2_base, c, s);
+        int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+        for (int hd = 0; hd < heads; ++hd) {
+            T *p = x + (size_t)row * row_stride + (size_t)hd * head_stride + first;
+            float u = to_f(p[a]), v = to_f(p[b]);
+            p[a] = from_f<T>(u * c - v * s);
+            p[b] = from_f<T>(v * c + u * s);
+        }
+    }
+}
+
+template <typename T>
+__global__ void latent_append_kernel(const T *__restrict__ down, const T *__restrict__ norm_w, float eps, int rank, int rot, int rot_dims,
+                                     int interleaved, double log2_base, const int32_t *__restrict__ tok_pos, const int32_t *__restrict__ tok_seq,
+                                     const int32_t *__restrict__ block_table, int max_pages, int num_pages, int page_size, T *__restrict__ slab) {
+    __shared__ float scratch[33];
+    int t = blockIdx.x;
+    int pos = tok_pos[t];
+    int width = rank + rot;
+    const T *src = down + (size_t)t * width;
+    int page = block_table[(size_t)tok_seq[t] * max_pages + pos / page_size];
+    bool ok = page >= 0 && page < num_pages;  // a bad table entry drops the write instead of corrupting another page
+    T *dst = slab + ((size_t)(ok ? page : 0) * page_size + pos % page_size) * width;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+        float v = to_f(src[d]);
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    if (!ok) return;
+    float inv = 1.0f / sqrtf(ss / (float)rank + eps);
+    for (int d = threadIdx.x; d < rank; d += blockDim.x) dst[d] = from_f<T>(to_f(src[d]) * inv * to_f(norm_w[d]));
+    int half = rot_dims / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float c, s;
+        rope_angle(pos, i, rot_dims, log2_base, c, s);
+        int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+        float u = to_f(src[rank + a]), v = to_f(src[rank + b]);
+        dst[rank + a] = from_f<T>(u * c - v * s);
+        dst[rank + b] = from_f<T>(v * c + u * s);
+    }
+    for (int d = rot_dims + threadIdx.x; d < rot; d += blockDim.x) dst[rank + d] = src[rank + d];  // entries past the rotated ones pass
+}
+
+__device__ __forceinline__ float act_apply(float z, int act) {
+    if (act == 0) return z / (1.0f + expf(-z));
+    float inner = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+    return 0.5f * z * (1.0f + tanhf(inner));
+}
+
+template <typename T>
+__global__ void gated_act_kernel(const T *__restrict__ gu, T *__restrict__ out, long long total, int width, int act) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    long long row = i / width;
+    int j = (int)(i - row * width);
+    float g = to_f(gu[row * 2 * width + j]), u = to_f(gu[row * 2 * width + width + j]);
+    out[i] = from_f<T>(act_apply(g, act) * u);
+}
+
+__global__ void argmax_rows_kernel(const float *__restrict__ logits, int32_t *__restrict__ out, int vocab) {
+    __shared__ float best_v[32];
+    __shared__ int best_i[32];
+    const float *row = logits + (size_t)blockIdx.x * vocab;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int j = threadIdx.x; j < vocab; j += blockDim.x) {
+        float v = row[j];
+        if (v > bv || (v == bv && j < bi)) bv = v, bi = j;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+    }
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) best_v[warp] = bv, best_i[warp] = bi;
+    __syncthreads();
+    if (warp == 0) {
+        int n = blockDim.x >> 5;
+        bv = lane < n ? best_v[lane] : -INFINITY;
+        bi = lane < n ? best_i[lane] : 0x7fffffff;
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+        }
+        if (lane == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
+}  // namespace tlb
+
+using namespace tlb;
+
+extern "C" {
+
+int tlb_abi_version(void) { return 1; }
+const char *tlb_last_error(void) { return tl::g_error; }
+long long tlb_launch_count(void) { return tl::g_launches.load(std::memory_order_relaxed); }
+
+int tlb_embed_rows(const int32_t *ids, const void *table, float *x32, void *h, int tokens, int vocab, int dim, int dtype, void *stream) {
+    if (tokens <= 0) return TL_OK;
+    if (!ids || !table || !x32 || vocab <= 0 || dim <= 0) return tl::fail(TL_EINVAL, "embed_rows: bad argument");
+    TLB_DISPATCH(dtype, "embed_rows",
+                 embed_rows_kernel<T><<<tokens, 256, 0, as_stream(stream)>>>(ids, (const T *)table, x32, (T *)h, vocab, dim));
+    TL_LAUNCH_CHECK("embed_rows");
+    return TL_OK;
+}
+
+int tlb_norm_residual(const void *y, int y_is_f32, const void *w, float weight_offset, const void *scale, float eps, float *residual, void *h,
+                      int rows, int dim, int dtype, void *stream) {
+    if (rows <= 0) return TL_OK;
+    if (!y || !w || dim <= 0 || (!residual && !h)) return tl::fail(TL_EINVAL, "norm_residual: bad argument");
+    int threads = dim >= 1024 ? 512 : 256;
+    TLB_DISPATCH(dtype, "norm_residual",
+                 if (y_is_f32) norm_residual_kernel<T, float><<<rows, threads, 0, as_stream(stream)>>>((const float *)y, (const T *)w, weight_offset,
+                                                                                                        (const T *)scale, eps, residual, (T *)h, dim);
+                 else norm_residual_kernel<T, T><<<rows, threads, 0, as_stream(stream)>>>((const T *)y, (const T *)w, weight_offset, (const T *)scale,
+                                                                                         eps, residual, (T *)h, dim));
+    TL_LAUNCH_CHECK("norm_residual");
+    return TL_OK;
+}
+
+int tlb_rope_rows(void *x, long long row_stride, long long head_stride, int first, int heads, int dims, int interleaved, double base,
+                  const int32_t *tok_pos, int rows, int dtype, void *stream) {
+    if (rows <= 0 || dims <= 0) return TL_OK;
+    if (!x || !tok_pos || heads <= 0 || (dims & 1) || base <= 0) return tl::fail(TL_EINVAL, "rope_rows: bad argument");
+    double lb = log2(base);
+    TLB_DISPATCH(dtype, "rope_rows",
+                 rope_rows_kernel<T><<<rows, 64, 0, as_stream(stream)>>>((T *)x, row_stride, head_stride, first, heads, dims, interleaved, lb, tok_pos));
+    TL_LAUNCH_CHECK("rope_rows");
+    return TL_OK;
+}
+
+int tlb_latent_append(const void *down, const void *norm_w, float eps, int rank, int rot, int rot_dims, int interleaved, double base,
+                      const int32_t *tok_pos, const int32_t *tok_seq, const int32_t *block_table, int max_pages, int num_pages, int page_size,
+                      void *slab, int tokens, int dtype, void *stream) {
+    if (tokens <= 0) return TL_OK;
+    if (!down || !norm_w || !tok_pos || !tok_seq || !block_table || !slab || rank <= 0 || rot < 0 || rot_dims > rot || (rot_dims & 1) ||
+        page_size <= 0 || max_pages <= 0 || base <= 0)
+        return tl::fail(TL_EINVAL, "latent_append: bad argument");
+    double lb = log2(base);
+    TLB_DISPATCH(dtype, "latent_append",
+                 latent_append_kernel<T><<<tokens, 128, 0, as_stream(stream)>>>((const T *)down, (const T *)norm_w, eps, rank, rot, rot_dims, interleaved,
+                                                                               lb, tok_pos, tok_seq, block_table, max_pages, num_pages, page_size,
+                                                                               (T *)slab));
+    TL_LAUNCH_CHECK("latent_append");
+    return TL_OK;
+}
+
+int tlb_gated_act(const void *gu, void *out, int rows, int width, int act, int dtype, void *stream) {
+    if (rows <= 0 || width <= 0) return TL_OK;
+    if (!gu || !out || (act != 0 && act != 1)) return tl::fail(TL_EINVAL, "gated_act: bad argument");
+    long long total = (long long)rows * width;
+    TLB_DISPATCH(dtype, "gated_act",
+                 gated_act_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>((const T *)gu, (T *)out, total, width, act));
+    TL_LAUNCH_CHECK("gated_act");
+    return TL_OK;
+}
+
+int tlb_argmax_rows(const float *logits, int32_t *out, int rows, int vocab, void *stream) {
+    if (rows <= 0) return TL_OK;
+    if (!logits || !out || vocab <= 0) return tl::fail(TL_EINVAL, "argmax_rows: bad argument");
+    argmax_rows_kernel<<<rows, 256, 0, as_stream(stream)>>>(logits, out, vocab);
+    TL_LAUNCH_CHECK("argmax_rows");
+    return TL_OK;
+}
+
+}  // extern "C"

@@ -38,6 +38,15 @@ SOURCES = [
     "decode_attention_fused.cu",
 ]
 
+# The second library: building blocks for models with unquantised weights (include/tiny_llm_b200_blocks.h).  It links
+# on its own, so a process that runs only such a model compiles these few files and nothing of the W4A16 path.
+BLOCKS_LIB = OUT_DIR / f"libtiny_llm_b200_blocks{SUFFIX}.so"
+BLOCKS_SOURCES = [
+    "blocks/blocks_rows.cu",
+    "blocks/blocks_latent_attention.cu",
+    "blocks/blocks_moe.cu",
+]
+
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -51,7 +60,10 @@ FLAGS = [
 
 def _digest(path: Path) -> str:
     h = hashlib.sha256()
-    for dep in sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + [ROOT / "include" / "tiny_llm_b200.h", path]):
+    headers = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list((ROOT / "include").glob("*.h"))
+    if path.parent != CSRC:
+        headers += list(path.parent.glob("*.cuh"))
+    for dep in sorted(headers + [path]):
         h.update(dep.read_bytes())
     h.update(" ".join(FLAGS).encode())
     return h.hexdigest()
@@ -64,7 +76,8 @@ def _compile(src: str, verbose: bool) -> Path:
     want = _digest(path)
     if obj.exists() and stamp.exists() and stamp.read_text() == want:
         return obj
-    cmd = [NVCC, *FLAGS, "-c", str(path), "-o", str(obj)]
+    part = obj.with_name(f".{obj.name}.{os.getpid()}")
+    cmd = [NVCC, *FLAGS, "-c", str(path), "-o", str(part)]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     proc = subprocess.run(cmd, capture_output=True, text=True)
@@ -73,25 +86,40 @@ def _compile(src: str, verbose: bool) -> Path:
         raise RuntimeError(f"nvcc failed on {src}")
     if verbose:
         sys.stderr.write(proc.stderr)
+    os.replace(part, obj)
     stamp.write_text(want)
     return obj
 
 
-def build(verbose: bool = False) -> Path:
+def _link(lib: Path, sources: list, verbose: bool) -> Path:
     BUILD.mkdir(exist_ok=True)
     OUT_DIR.mkdir(parents=True, exist_ok=True)
-    with ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as pool:
-        objs = list(pool.map(lambda s: _compile(s, verbose), SOURCES))
+    with ThreadPoolExecutor(max_workers=min(8, len(sources))) as pool:
+        objs = list(pool.map(lambda s: _compile(s, verbose), sources))
     newest = max(o.stat().st_mtime for o in objs)
-    if not LIB.exists() or LIB.stat().st_mtime < newest:
+    if not lib.exists() or lib.stat().st_mtime < newest:
+        # link beside the target and rename: another process may be loading or building the same library
+        part = lib.with_name(f".{lib.name}.{os.getpid()}")
         cmd = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static",
-               "-o", str(LIB), *map(str, objs), "-lcuda"]
+               "-o", str(part), *map(str, objs), "-lcuda"]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             sys.stderr.write(proc.stdout + proc.stderr)
             raise RuntimeError("link failed")
-    return LIB
+        os.replace(part, lib)
+    return lib
+
+
+def build_blocks(verbose: bool = False) -> Path:
+    """libtiny_llm_b200_blocks.so alone (seconds)."""
+    return _link(BLOCKS_LIB, BLOCKS_SOURCES, verbose)
+
+
+def build(verbose: bool = False) -> Path:
+    """Both libraries; returns the W4A16 one."""
+    build_blocks(verbose)
+    return _link(LIB, SOURCES, verbose)
 
 
 if __name__ == "__main__":
-    print(build(verbose="-v" in sys.argv))
+    print((build_blocks if "--blocks" in sys.argv else build)(verbose="-v" in sys.argv))

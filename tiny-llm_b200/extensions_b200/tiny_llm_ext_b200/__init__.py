@@ -785,4 +785,21 @@ def device_info() -> tuple[int, int, int]:
 
 
 # TL_LIB selects an experiment build (tiny-llm_b200/csrc/build.py with TL_LIB_SUFFIX); default: the in-tree product library.
-load_library(os.environ.get("TL_LIB") or None)
+class _NotBuilt:
+    """Stands in for the library handle while ``libtiny_llm_b200.so`` has not been built: importing the package stays
+    possible (a process that only runs models of the blocks library never needs the W4A16 kernels), and the first
+    call into this module raises the ``ImportError`` that ``load_library`` would have raised."""
+
+    def __init__(self, error: ImportError):
+        self._error = error
+
+    def __getattr__(self, name):
+        raise ImportError(str(self._error))
+
+
+try:
+    load_library(os.environ.get("TL_LIB") or None)
+except ImportError as _missing:
+    if os.environ.get("TL_LIB"):
+        raise
+    _lib = _NotBuilt(_missing)

@@ -1,0 +1,249 @@
+"""ctypes binding of ``libtiny_llm_b200_blocks.so`` (C ABI: ``include/tiny_llm_b200_blocks.h``): row-wise norms over
+an fp32 residual stream, rotary positions, the paged latent cache, latent attention over ragged batches, gated
+activations and the mixture-of-experts kernels.  Arguments are contiguous CUDA ``torch.Tensor`` s (strided where the
+function says so); every call enqueues on the current stream.  There is no CPU path.
+
+The library is built on first use when it is missing (three small translation units, a few seconds of nvcc)."""
+
+from __future__ import annotations
+
+import ctypes
+import importlib.util
+import os
+from pathlib import Path
+
+import torch
+
+_HERE = Path(__file__).resolve().parent
+_LIB_NAME = "libtiny_llm_b200_blocks.so"
+_lib = None
+
+_VP, _I, _F, _D, _LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_double, ctypes.c_longlong
+
+_SIGNATURES = {
+    "tlb_abi_version": (_I, []),
+    "tlb_last_error": (ctypes.c_char_p, []),
+    "tlb_launch_count": (_LL, []),
+    "tlb_embed_rows": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _VP]),
+    "tlb_norm_residual": (_I, [_VP, _I, _VP, _F, _VP, _F, _VP, _VP, _I, _I, _I, _VP]),
+    "tlb_rope_rows": (_I, [_VP, _LL, _LL, _I, _I, _I, _I, _D, _VP, _I, _I, _VP]),
+    "tlb_latent_append": (_I, [_VP, _VP, _F, _I, _I, _I, _I, _D, _VP, _VP, _VP, _I, _I, _I, _VP, _I, _I, _VP]),
+    "tlb_latent_attention": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _VP, _LL, _LL, _I, _VP]),
+    "tlb_gated_act": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
+    "tlb_moe_route": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _VP, _VP, _I, _VP]),
+    "tlb_moe_max_rows": (_LL, [_I, _I, _I]),
+    "tlb_moe_sort": (_I, [_VP, _I, _I, _I, _VP, _VP, _VP, _VP]),
+    "tlb_moe_gate_up": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _VP, _I, _VP]),
+    "tlb_moe_down": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I, _VP]),
+    "tlb_moe_combine": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _VP]),
+    "tlb_argmax_rows": (_I, [_VP, _VP, _I, _I, _VP]),
+}
+EXPORTED_SYMBOLS = tuple(_SIGNATURES)
+
+ATTENTION_TILE_TOKENS = 4
+MOE_TILE_ROWS = 32
+ACT_SILU, ACT_GELU_TANH = 0, 1
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 2}
+
+
+def _build() -> Path:
+    script = _HERE.parent.parent / "csrc" / "build.py"
+    spec = importlib.util.spec_from_file_location("tiny_llm_b200_build", script)
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module.build_blocks()
+
+
+def load_library(path: str | os.PathLike | None = None) -> None:
+    """Load the library, compiling it first when the in-tree file is missing (``ImportError`` if that fails)."""
+    global _lib
+    candidate = Path(path) if path is not None else _HERE / _LIB_NAME
+    if not candidate.exists():
+        if path is not None:
+            raise ImportError(f"{candidate} not found")
+        try:
+            candidate = _build()
+        except Exception as exc:  # no nvcc, read-only tree, compile error
+            raise ImportError(f"{candidate} is not built and could not be compiled: {exc}") from exc
+    lib = ctypes.CDLL(str(candidate))
+    for name, (restype, argtypes) in _SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+
+
+def library():
+    if _lib is None:
+        load_library(os.environ.get("TL_BLOCKS_LIB") or None)
+    return _lib
+
+
+def launch_count() -> int:
+    return int(library().tlb_launch_count())
+
+
+def _code(t: torch.dtype) -> int:
+    if t not in _DTYPE_CODE:
+        raise RuntimeError(f"blocks: dtype {t} is not float32 or bfloat16")
+    return _DTYPE_CODE[t]
+
+
+def _gpu(op: str, *tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(f"{op}: the blocks extension is GPU-only")
+
+
+def _contig(op: str, *tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_contiguous():
+            raise RuntimeError(f"{op}: arguments must be contiguous")
+
+
+def _ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(ref: torch.Tensor) -> int:
+    return torch.cuda.current_stream(ref.device).cuda_stream
+
+
+def _check(code: int) -> None:
+    if code != 0:
+        raise RuntimeError(library().tlb_last_error().decode() or f"tiny_llm_b200_blocks error {code}")
+
+
+def embed_rows(ids: torch.Tensor, table: torch.Tensor):
+    """-> (x32 [T, D] fp32 residual stream, h [T, D] in the table's dtype)."""
+    _gpu("embed_rows", ids, table)
+    _contig("embed_rows", ids, table)
+    if ids.dtype != torch.int32 or ids.dim() != 1 or table.dim() != 2:
+        raise RuntimeError("embed_rows: ids must be int32 [T] and table [vocab, dim]")
+    T, (V, D) = ids.numel(), table.shape
+    x32 = torch.empty((T, D), dtype=torch.float32, device=table.device)
+    h = torch.empty((T, D), dtype=table.dtype, device=table.device)
+    _check(library().tlb_embed_rows(_ptr(ids), _ptr(table), _ptr(x32), _ptr(h), T, V, D, _code(table.dtype), _stream(table)))
+    return x32, h
+
+
+def norm_residual(y, weight, eps: float, *, weight_offset: float = 0.0, scale=None, residual=None, want_h: bool = True):
+    """RMS norm of ``y [rows, dim]`` (fp32 or the weight's dtype) times ``weight + weight_offset`` (times ``scale``);
+    with ``residual`` (fp32, updated in place) the result is added to it.  Returns the (new residual, or the norm)
+    rounded to the weight's dtype, or None when ``want_h`` is false."""
+    _gpu("norm_residual", y, weight, scale, residual)
+    _contig("norm_residual", y, weight, scale, residual)
+    rows, dim = y.shape
+    if y.dtype not in (torch.float32, weight.dtype):
+        raise RuntimeError("norm_residual: y must be float32 or the weight's dtype")
+    if weight.shape != (dim,) or (scale is not None and (scale.shape != (dim,) or scale.dtype != weight.dtype)):
+        raise RuntimeError("norm_residual: weight / scale must be [dim] of one dtype")
+    if residual is not None and (residual.dtype != torch.float32 or residual.shape != y.shape):
+        raise RuntimeError("norm_residual: residual must be float32 of y's shape")
+    if residual is None and not want_h:
+        raise RuntimeError("norm_residual: nothing to write")
+    h = torch.empty((rows, dim), dtype=weight.dtype, device=y.device) if want_h else None
+    _check(library().tlb_norm_residual(_ptr(y), int(y.dtype == torch.float32), _ptr(weight), float(weight_offset), _ptr(scale), float(eps),
+                                       _ptr(residual), _ptr(h), rows, dim, _code(weight.dtype), _stream(y)))
+    return h
+
+
+def rope_rows(x: torch.Tensor, tok_pos: torch.Tensor, *, heads: int, head_stride: int, first: int, dims: int, base: float, interleaved: bool):
+    """Rotate, in place, ``dims`` entries from ``first`` in each of ``heads`` heads of every row of ``x [rows, *]``."""
+    _gpu("rope_rows", x, tok_pos)
+    if x.dim() != 2 or x.stride(1) != 1 or tok_pos.dtype != torch.int32 or tok_pos.numel() != x.shape[0]:
+        raise RuntimeError("rope_rows: x must be [rows, n] with unit inner stride and tok_pos int32 [rows]")
+    if first + dims > head_stride or (heads - 1) * head_stride + first + dims > x.shape[1]:
+        raise RuntimeError("rope_rows: rotated entries fall outside the row")
+    _check(library().tlb_rope_rows(_ptr(x), x.stride(0), head_stride, first, heads, dims, int(interleaved), float(base), _ptr(tok_pos), x.shape[0],
+                                   _code(x.dtype), _stream(x)))
+    return x
+
+
+def latent_append(down, norm_weight, eps, *, rank, rot_dims, interleaved, base, tok_pos, tok_seq, block_table, slab):
+    """Norm the latent, rotate the shared key part and store both at every token's slot of ``slab [P, page, rank+rot]``."""
+    _gpu("latent_append", down, norm_weight, tok_pos, tok_seq, block_table, slab)
+    _contig("latent_append", down, norm_weight, tok_pos, tok_seq, block_table, slab)
+    T, width = down.shape
+    P, page_size, w2 = slab.shape
+    if w2 != width or slab.dtype != down.dtype or norm_weight.dtype != down.dtype or norm_weight.numel() != rank:
+        raise RuntimeError("latent_append: slab / weight do not match the projection")
+    if block_table.dtype != torch.int32 or block_table.dim() != 2 or tok_pos.numel() != T or tok_seq.numel() != T:
+        raise RuntimeError("latent_append: bad metadata")
+    _check(library().tlb_latent_append(_ptr(down), _ptr(norm_weight), float(eps), rank, width - rank, rot_dims, int(interleaved), float(base),
+                                       _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), block_table.shape[1], P, page_size, _ptr(slab), T,
+                                       _code(down.dtype), _stream(down)))
+
+
+def latent_attention(q_lat, q_rot, slab, block_table, tiles, tok_pos, *, window: int, scale: float, out):
+    """``q_lat [T, H, rank]``, ``q_rot [T, H, rot]`` and ``out [T, H, rank]`` are views with arbitrary token / head strides
+    and unit inner stride; ``tiles [n, 3]`` int32 (first token, count, block-table row)."""
+    _gpu("latent_attention", q_lat, q_rot, slab, block_table, tiles, tok_pos, out)
+    _contig("latent_attention", slab, block_table, tiles, tok_pos)
+    T, H, rank = q_lat.shape
+    P, page_size, width = slab.shape
+    rot = width - rank
+    if q_rot.shape != (T, H, rot) or out.shape != (T, H, rank) or q_lat.stride(2) != 1 or q_rot.stride(2) != 1 or out.stride(2) != 1:
+        raise RuntimeError("latent_attention: query / output shapes do not match the cache")
+    if not (q_lat.dtype == q_rot.dtype == slab.dtype == out.dtype):
+        raise RuntimeError("latent_attention: one dtype for queries, cache and output")
+    _check(library().tlb_latent_attention(_ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(slab), P,
+                                          page_size, rank, rot, _ptr(block_table), block_table.shape[1], _ptr(tiles), tiles.shape[0], _ptr(tok_pos),
+                                          H, int(window or 0), float(scale), _ptr(out), out.stride(0), out.stride(1), _code(slab.dtype), _stream(slab)))
+    return out
+
+
+def gated_act(gate_up: torch.Tensor, act: int) -> torch.Tensor:
+    """``act(gate) * up`` of ``[rows, 2 * width]`` (gate columns first)."""
+    _gpu("gated_act", gate_up)
+    _contig("gated_act", gate_up)
+    rows, two = gate_up.shape
+    out = torch.empty((rows, two // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _check(library().tlb_gated_act(_ptr(gate_up), _ptr(out), rows, two // 2, act, _code(gate_up.dtype), _stream(gate_up)))
+    return out
+
+
+def moe_route(h, router_w, router_b, top: int):
+    _gpu("moe_route", h, router_w, router_b)
+    _contig("moe_route", h, router_w, router_b)
+    T, D = h.shape
+    E = router_w.shape[0]
+    idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
+    gate = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    _check(library().tlb_moe_route(_ptr(h), _ptr(router_w), _ptr(router_b), T, D, E, top, _ptr(idx), _ptr(gate), _code(h.dtype), _stream(h)))
+    return idx, gate
+
+
+def moe_experts(h, idx, gate, w_gate, w_up, w_down, act: int, shared=None) -> torch.Tensor:
+    """Weighted sum of the chosen experts' gated feed-forwards (+ ``shared [T, D]``) -> fp32 ``[T, D]``.
+    ``w_gate, w_up [E, ff, D]``, ``w_down [E, D, ff]``."""
+    _gpu("moe_experts", h, idx, gate, w_gate, w_up, w_down, shared)
+    _contig("moe_experts", h, idx, gate, w_gate, w_up, w_down, shared)
+    lib = library()
+    T, D = h.shape
+    E, ff, _ = w_gate.shape
+    top = idx.shape[1]
+    max_rows = int(lib.tlb_moe_max_rows(T, top, E))
+    dev, code, st = h.device, _code(h.dtype), _stream(h)
+    sorted_pair = torch.empty(max_rows, dtype=torch.int32, device=dev)
+    tile_expert = torch.empty(max_rows // MOE_TILE_ROWS, dtype=torch.int32, device=dev)
+    counters = torch.empty(2, dtype=torch.int32, device=dev)
+    inter = torch.empty((max_rows, ff), dtype=h.dtype, device=dev)
+    pair_out = torch.empty((T * top, D), dtype=torch.float32, device=dev)
+    y = torch.empty((T, D), dtype=torch.float32, device=dev)
+    _check(lib.tlb_moe_sort(_ptr(idx), T, top, E, _ptr(sorted_pair), _ptr(tile_expert), _ptr(counters), st))
+    _check(lib.tlb_moe_gate_up(_ptr(h), _ptr(w_gate), _ptr(w_up), _ptr(sorted_pair), _ptr(tile_expert), _ptr(counters), T, top, E, D, ff, act,
+                               _ptr(inter), code, st))
+    _check(lib.tlb_moe_down(_ptr(inter), _ptr(w_down), _ptr(sorted_pair), _ptr(tile_expert), _ptr(counters), T, top, E, D, ff, _ptr(pair_out), code, st))
+    _check(lib.tlb_moe_combine(_ptr(pair_out), _ptr(gate), _ptr(shared), _ptr(y), T, top, D, code, st))
+    return y
+
+
+def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
+    _gpu("argmax_rows", logits)
+    _contig("argmax_rows", logits)
+    if logits.dtype != torch.float32 or logits.dim() != 2:
+        raise RuntimeError("argmax_rows: expected float32 [rows, vocab]")
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    _check(library().tlb_argmax_rows(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1], _stream(logits)))
+    return out

@@ -45,6 +45,11 @@ def _read_tensors(path: Path) -> dict:
     return tensors
 
 
+def read_tensors(path) -> dict:
+    """Every tensor of the ``*.safetensors`` files of a checkpoint directory, by name, on the CPU."""
+    return _read_tensors(Path(path))
+
+
 def load_checkpoint(path, device="cpu") -> SimpleNamespace:
     """``mlx_lm.load(path)[0]`` as far as the tiny-llm models look at it."""
     path = Path(path)

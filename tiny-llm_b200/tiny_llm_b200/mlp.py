@@ -1,0 +1,58 @@
+"""Gated feed-forward layers with unquantised weights: ``down(act(gate x) * (up x))``.
+
+``GatedMLP`` is the dense form (gate and up stacked into one product, the activation fused with the gating product in
+one launch); ``TopKRouter`` + ``MixtureOfExperts`` the sparse one: router logits in fp32, the ``top`` largest chosen,
+softmax over the chosen logits only, the chosen experts' outputs summed with those weights, optionally plus a shared
+expert that every token takes.  The expert products are grouped GEMMs of the blocks library over a device-built
+list of (token, choice) pairs sorted by expert: no host synchronisation, and a token's result does not depend on the
+rest of the batch."""
+
+from __future__ import annotations
+
+import torch
+
+from .basics import linear
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+class GatedMLP:
+    def __init__(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, act: str):
+        self.w_gate_up = torch.cat([w_gate, w_up], dim=0).contiguous()  # [2 ff, D]: one product for both
+        self.w_down = w_down.contiguous()
+        self.act = ACTIVATIONS[act]
+
+    def __call__(self, h: torch.Tensor) -> torch.Tensor:
+        from extensions_b200.tiny_llm_ext_b200 import blocks
+
+        return linear(blocks.gated_act(linear(h, self.w_gate_up), self.act), self.w_down)
+
+
+class TopKRouter:
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None, top: int):
+        self.weight, self.bias, self.top = weight.contiguous(), None if bias is None else bias.contiguous(), int(top)
+        if not 0 < self.top <= weight.shape[0]:
+            raise ValueError(f"router: top={top} of {weight.shape[0]} experts")
+
+    def __call__(self, h: torch.Tensor):
+        """-> (expert ids int32 [T, top], weights fp32 [T, top])."""
+        from extensions_b200.tiny_llm_ext_b200 import blocks
+
+        return blocks.moe_route(h, self.weight, self.bias, self.top)
+
+
+class MixtureOfExperts:
+    def __init__(self, router: TopKRouter, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, act: str,
+                 shared: GatedMLP | None = None):
+        """``w_gate, w_up [E, ff, D]``, ``w_down [E, D, ff]`` (the experts stacked)."""
+        self.router, self.shared = router, shared
+        self.w_gate, self.w_up, self.w_down = w_gate.contiguous(), w_up.contiguous(), w_down.contiguous()
+        self.act = ACTIVATIONS[act]
+
+    def __call__(self, h: torch.Tensor) -> torch.Tensor:
+        """-> fp32 [T, D]."""
+        from extensions_b200.tiny_llm_ext_b200 import blocks
+
+        idx, gate = self.router(h)
+        shared = None if self.shared is None else self.shared(h)
+        return blocks.moe_experts(h, idx, gate, self.w_gate, self.w_up, self.w_down, self.act, shared)

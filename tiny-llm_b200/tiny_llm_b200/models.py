@@ -13,6 +13,41 @@ MODEL_SHORTCUTS = {
 }
 
 
+# Designs that describe themselves in config.json (key "architecture"): name -> class with
+# ``from_checkpoint(config, tensors, dtype=, device=, **kwargs)``.  Imported on demand: a process that runs one design
+# loads (and, for the native libraries, builds) only what that design uses.
+ARCHITECTURES = {"Voluzen": ("tiny_llm_b200.voluzen", "VoluzenModel")}
+
+
+def model_class(architecture: str):
+    import importlib
+
+    if architecture not in ARCHITECTURES:
+        raise ValueError(f"architecture {architecture!r} is not supported (known: {sorted(ARCHITECTURES)})")
+    module, name = ARCHITECTURES[architecture]
+    return getattr(importlib.import_module(module), name)
+
+
+def load_model(path, device="cuda", dtype=None, **kwargs):
+    """Model object for a checkpoint DIRECTORY, chosen by its config.json: a self-describing design
+    (``architecture``) is built by its class from the plain tensors; an MLX 4-bit Qwen3 checkpoint goes through
+    ``load_checkpoint`` + ``dispatch_model`` (week 3)."""
+    import json
+    from pathlib import Path
+
+    import torch
+
+    config = json.loads((Path(path) / "config.json").read_text())
+    if "architecture" in config:
+        from .checkpoint import read_tensors
+
+        cls = model_class(config["architecture"])
+        return cls.from_checkpoint(config, read_tensors(path), device=device, dtype=dtype or torch.bfloat16, **kwargs)
+    from .checkpoint import load_checkpoint
+
+    return dispatch_model("Qwen/Qwen3-" + str(path), load_checkpoint(path, device=device), week=3, **kwargs)
+
+
 def shortcut_name_to_full_name(name: str) -> str:
     return MODEL_SHORTCUTS.get(name.lower(), name)
 

@@ -1,0 +1,90 @@
+"""Ragged batches: one model step over several requests, each bringing any number of new tokens.
+
+A continuous-batching step is a flat list of tokens: a portion of one request's prompt beside single decoded tokens of
+others.  ``RaggedEntry`` names one request's share, ``RaggedPlan`` is what the kernels need, built on the host from the
+requests' page lists and moved to the device as ONE pinned block:
+
+    ids [T] | tok_pos [T] | tok_seq [T] | want_rows [W] | tiles [n, 3] | block_table [S, max_pages]
+
+``tok_pos`` is the position of a token in its sequence, ``tok_seq`` its row in this step's block table, ``tiles`` the
+attention kernel's work list (runs of at most ``tile`` consecutive tokens of one sequence).  Building the plan also
+does the step's cache bookkeeping: every request's page list grows by its new tokens (pages come from the pool's free
+list first), before anything is launched.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class RaggedEntry:
+    tokens: Sequence[int]
+    cache: list                       # the request's per-layer caches (model.create_kv_cache())
+    want: Sequence[int] | None = None  # places among `tokens` whose logits are wanted; None = the last one
+
+
+class RaggedPlan:
+    def __init__(self, entries: Sequence[RaggedEntry], device, tile: int):
+        owners = []
+        for e in entries:
+            if len(e.tokens) == 0:
+                raise ValueError("a ragged entry needs at least one token")
+            owner = getattr(e.cache[0], "owner", e.cache[0])
+            if any(owner is o for o in owners):
+                raise ValueError("a request may appear once per step")
+            owners.append(owner)
+        starts = [o.offset for o in owners]
+        done = []
+        try:
+            for o, e in zip(owners, entries):
+                o.append_slots(len(e.tokens))
+                done.append((o, len(e.tokens)))
+        except Exception:
+            for o, n in done:  # all-or-nothing: give the pages of this step back
+                o.rewind(n)
+            raise
+        T = sum(len(e.tokens) for e in entries)
+        S = len(entries)
+        max_pages = max(o.num_pages for o in owners)
+        wants = [list(e.want) if e.want is not None else [len(e.tokens) - 1] for e in entries]
+        W = sum(len(w) for w in wants)
+        n_tiles = sum(-(-len(e.tokens) // tile) for e in entries)
+        total = 3 * T + W + 3 * n_tiles + S * max_pages
+        host = torch.empty(max(total, 1), dtype=torch.int32, pin_memory=torch.cuda.is_available() and torch.device(device).type == "cuda")
+        buf = host.numpy()
+        ids, pos, seq = buf[0:T], buf[T : 2 * T], buf[2 * T : 3 * T]
+        want = buf[3 * T : 3 * T + W]
+        tiles = buf[3 * T + W : 3 * T + W + 3 * n_tiles].reshape(n_tiles, 3)
+        table = buf[3 * T + W + 3 * n_tiles : total].reshape(S, max_pages)
+        table[:] = -1
+        t = w = k = 0
+        for s, (e, o, start) in enumerate(zip(entries, owners, starts)):
+            n = len(e.tokens)
+            ids[t : t + n] = np.asarray(e.tokens, dtype=np.int64)
+            pos[t : t + n] = np.arange(start, start + n, dtype=np.int64)
+            seq[t : t + n] = s
+            for place in wants[s]:
+                if not 0 <= place < n:
+                    raise ValueError(f"wanted place {place} is outside the entry's {n} tokens")
+                want[w] = t + place
+                w += 1
+            for first in range(0, n, tile):
+                tiles[k] = (t + first, min(tile, n - first), s)
+                k += 1
+            table[s, : o.num_pages] = o.page_ids
+            t += n
+        self.num_tokens, self.num_seqs, self.num_want, self.num_tiles, self.max_pages = T, S, W, n_tiles, max_pages
+        self.h2d_bytes = total * 4
+        dev = host.to(device, non_blocking=True)
+        self._host = host  # keep the pinned block alive until the copy has run
+        self.ids, self.tok_pos, self.tok_seq = dev[0:T], dev[T : 2 * T], dev[2 * T : 3 * T]
+        self.want_rows = dev[3 * T : 3 * T + W]
+        self.tiles = dev[3 * T + W : 3 * T + W + 3 * n_tiles].view(n_tiles, 3)
+        self.block_table = dev[3 * T + W + 3 * n_tiles : total].view(S, max_pages)
+        self.want_counts = [len(x) for x in wants]
+        self.starts = starts
