@@ -155,3 +155,25 @@ def forward(config, weights, tokens, dtype=torch.float64, return_layers=False):
         stream.append(x)
     logits = norm_zero_centred(x, w["final.norm"], eps) @ w["head"].T
     return (logits, torch.stack(stream)) if return_layers else logits
+
+
+def cache_attention(q_full, rows, positions, rank, window, scale):
+    """Multi-query attention straight on cache rows: query ``q_full [T, H, rank+rot]`` at ``positions`` against keys
+    ``rows [S, rank+rot]`` (key j at position j), values = the first ``rank`` entries of the rows."""
+    scores = torch.einsum("thd,jd->thj", q_full, rows) * scale
+    j = torch.arange(rows.shape[0])[None, :]
+    p = positions[:, None]
+    keep = j <= p
+    if window:
+        keep = keep & (p - j < window)
+    scores = scores.masked_fill(~keep[:, None, :], float("-inf"))
+    return torch.einsum("thj,jr->thr", torch.softmax(scores, dim=-1), rows[:, :rank])
+
+
+def greedy(config, weights, prompt, steps):
+    """Greedy continuation by full recomputation."""
+    ids, out = list(prompt), []
+    for _ in range(steps):
+        ids.append(int(forward(config, weights, ids)[-1].argmax()))
+        out.append(ids[-1])
+    return out

@@ -30,6 +30,12 @@ def greedy_tokens(logits: torch.Tensor) -> torch.Tensor:
     subtracts logsumexp first (batch.py:10-12), which cannot change the argmax;
     CUDA logits use the extension's reduction kernel, host tensors (fake models
     in scheduler tests) plain torch."""
+    if logits.is_cuda and logits.dtype == torch.float32:
+        # fp32 rows come from the models of the blocks library, which has its own reduction (so that such a model
+        # does not need the W4A16 library to be built)
+        from extensions_b200.tiny_llm_ext_b200 import blocks
+
+        return blocks.argmax_rows(logits.contiguous())
     if logits.is_cuda:
         return tiny_llm_ext_b200.argmax(logits.contiguous())
     return torch.argmax(logits, dim=-1)
@@ -164,7 +170,7 @@ class ContinuousBatcher:
     """The reference scheduling loop as a steppable object."""
 
     def __init__(self, model, tokenizer, prompts, max_seq_len=512, batch_size=5, prefill_step=128, verbose=True,
-                 eos_token_id=None, device=None, max_new_tokens=None):
+                 eos_token_id=None, device=None, max_new_tokens=None, mixed=None):
         if max_seq_len <= 0:
             raise ValueError("max_seq_len must be positive")
         if batch_size <= 0:
@@ -181,6 +187,13 @@ class ContinuousBatcher:
         self.eos_token_id = eos_token_id
         self.device = device
         self.max_new_tokens = max_new_tokens  # optional per-request budgets (synthetic serving)
+        # Mixed steps: a model with a ragged step (``forward_ragged``) takes the prompt portion of the request being
+        # prefilled and the single tokens of all decode slots as ONE batch per iteration, instead of one B = 1 prefill
+        # call followed by one decode call.  None = whenever the model can.
+        self.mixed = hasattr(model, "forward_ragged") if mixed is None else bool(mixed)
+        if self.mixed and not hasattr(model, "forward_ragged"):
+            raise ValueError("mixed steps need a model with forward_ragged")
+        self.mixed_steps = 0
         self.slots: list[Request | None] = [None] * batch_size
         self.kv_cache = [BatchingKvCache(max_active_requests=batch_size, max_seq_len=max_seq_len) for _ in range(model.num_hidden_layers)]
         self.pending: Request | None = None
@@ -244,7 +257,101 @@ class ContinuousBatcher:
         return self.generated.get(request.prompt_idx, 0) >= self.max_new_tokens[request.prompt_idx]
 
     # -- one scheduler iteration ----------------------------------------------
+    def _retire_or_seat(self, request: Request) -> bool:
+        """A request whose prompt is consumed either ends (done, length or budget) or takes the first idle slot."""
+        if request.is_done or request.reaches_max_seq_len(self.max_seq_len) or self._budget_spent(request):
+            text = request.text()
+            for layer_cache in request.kv_cache:
+                layer_cache.release()
+            self.results.append((request.prompt_idx, text))
+            self.pending = None
+            return True
+        for i in range(self.batch_size):
+            if self.slots[i] is None:
+                for layer_cache, table in zip(request.kv_cache, self.kv_cache):
+                    table.add_request(layer_cache, i)
+                self.slots[i] = request
+                self.pending = None
+                return True
+        return False
+
+    def _decoded(self, i: int, request: Request, token: int) -> None:
+        """Book one decoded token of slot ``i`` and free the slot when the request ends."""
+        request.decode_done(token)
+        self.decode_tokens += 1
+        self.generated[request.prompt_idx] = self.generated.get(request.prompt_idx, 0) + (0 if request.is_done else 1)
+        reason = None
+        if request.is_done:
+            reason = request.finish_reason
+        elif request.reaches_max_seq_len(self.max_seq_len):
+            reason = "max seq len"
+        elif self._budget_spent(request):
+            reason = "max new tokens"
+        if reason is not None:
+            if self.verbose:
+                print(f"Removing request {i} due to {reason}", flush=True)
+            text = request.text()
+            for table in self.kv_cache:
+                table.remove_request(i)
+            self.results.append((request.prompt_idx, text))
+            self.slots[i] = None
+
+    def _step_mixed(self) -> None:
+        """One iteration as ONE ragged batch: the next portion of the pending prompt beside one token per live slot."""
+        from .ragged import RaggedEntry
+
+        if self.queue and self.pending is None:
+            self.pending = Request(self.model, self.tokenizer, self.queue.pop(0), self.prefill_step, self.next_request_idx,
+                                   max_seq_len=self.max_seq_len, eos_token_id=self.eos_token_id, device="cpu")
+            self.next_request_idx += 1
+        request = self.pending
+        if request is not None and request.is_prefill_done:  # waited for a slot
+            if self._retire_or_seat(request):
+                self._progress()
+            request = self.pending
+        entries, chunk = [], 0
+        if request is not None and not request.is_prefill_done:
+            total = request.prefill_tokens.numel()
+            chunk = min(self.prefill_step, total - request.offset)
+            entries.append(RaggedEntry(request.prefill_tokens[request.offset : request.offset + chunk].tolist(), request.kv_cache))
+        live = [i for i, s in enumerate(self.slots) if s is not None]
+        for i in live:
+            entries.append(RaggedEntry([self.slots[i].next_token], [table.kv_caches[i] for table in self.kv_cache]))
+        if not entries:
+            return
+        if self.record_timing:
+            self._record_cache_state()
+        t0 = time.perf_counter() if self.record_timing else 0.0
+        span = self._gpu_span("decode" if live else "prefill")
+        host = greedy_tokens(self.model.forward_ragged(entries)).reshape(-1).tolist()  # one device->host read per step
+        if span is not None:
+            span.record()
+        if self.record_timing:
+            (self.decode_step_ms if live else self.prefill_chunk_ms).append((time.perf_counter() - t0) * 1e3)
+        self.mixed_steps += 1
+        if chunk:
+            request.offset += chunk
+            self.prefill_tokens += chunk
+            if request.offset == request.prefill_tokens.numel():
+                request.is_prefill_done = True
+                if self.max_seq_len is not None and request.offset >= self.max_seq_len:
+                    request.is_done, request.finish_reason = True, "max seq len"
+                else:
+                    request.decode_done(int(host[0]), False)
+                    if request.next_token is not None:
+                        self.generated[request.prompt_idx] = 1
+            host = host[1:]
+        if live:
+            self.decode_steps += 1
+        for i, token in zip(live, host):
+            self._decoded(i, self.slots[i], int(token))
+        if request is not None and request.is_prefill_done:
+            self._retire_or_seat(request)
+        self._progress()
+
     def step(self) -> None:
+        if self.mixed:
+            return self._step_mixed()
         if self.queue and self.pending is None:
             prompt = self.queue.pop(0)
             self.pending = Request(

@@ -6,6 +6,11 @@ see checkpoint.py; there is no hub download here).
     python -m tiny_llm_b200.cli generate --model /path/to/Qwen3-4B-MLX-4bit --prompt "..." [--loader week3]
     python -m tiny_llm_b200.cli batch    --model /path/to/ckpt --prompts-file prompts.txt --batch-size 5
     python -m tiny_llm_b200.cli generate --synthetic tiny-d128 --prompt-ids 5,17,3 --max-new-tokens 8   (no files needed)
+    python -m tiny_llm_b200.cli generate --synthetic voluzen:WCSM --prompt-ids 5,17,3 --max-new-tokens 8
+    python -m tiny_llm_b200.cli trace    --model DIR --dtype float32 --out DIR --max-tokens N < steps.jsonl   (trace_runner.py)
+
+A checkpoint whose config.json names its ``architecture`` (Voluzen) is built by that design's class
+(``models.load_model``); such models take ``--dtype`` and batch with mixed prefill + decode steps.
 """
 
 from __future__ import annotations
@@ -16,10 +21,38 @@ import sys
 import torch
 
 
+def _self_describing(args, device):
+    """The model object when --model / --synthetic name a design that config.json describes, else None."""
+    import json
+    from pathlib import Path
+
+    dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[args.dtype]
+    if args.synthetic and args.synthetic.startswith("voluzen"):
+        from .models import model_class
+        from .synthetic import synthetic_voluzen, voluzen_config
+
+        config = voluzen_config(pattern=args.synthetic.partition(":")[2] or "WCSM")
+        return model_class("Voluzen").from_checkpoint(config, synthetic_voluzen(config, seed=0), device=device, dtype=dtype)
+    if args.model and "architecture" in json.loads((Path(args.model) / "config.json").read_text()):
+        from .models import load_model
+
+        return load_model(args.model, device=device, dtype=dtype)
+    return None
+
+
 def _load(args, device):
     from .checkpoint import load_checkpoint, load_tokenizer
     from .synthetic import synthetic_qwen3
 
+    model = _self_describing(args, device)
+    if model is not None:
+        tokenizer = None
+        if args.model:
+            try:
+                tokenizer = load_tokenizer(args.model)
+            except Exception as exc:
+                print(f"(no tokenizer loaded from {args.model}: {exc})", file=sys.stderr)
+        return model, tokenizer, None
     if args.synthetic:
         return synthetic_qwen3(args.synthetic, seed=0, device=device, realistic=args.synthetic.startswith("tiny")), None, "Qwen/Qwen3-synthetic"
     ns = load_checkpoint(args.model, device=device)
@@ -34,6 +67,8 @@ def _load(args, device):
 def _model(args, ns, name):
     from .models import dispatch_model
 
+    if name is None:  # already a model object
+        return ns
     if args.loader == "week2":
         return dispatch_model(name, ns, week=2)
     return dispatch_model(name, ns, week=3, enable_paged_attention=not args.disable_paged_attention)
@@ -97,17 +132,23 @@ def cmd_batch(args) -> int:
 
 
 def main(argv=None) -> int:
+    argv = sys.argv[1:] if argv is None else list(argv)
+    if argv and argv[0] == "trace":
+        from .trace_runner import main as trace_main
+
+        return trace_main(argv[1:])
     ap = argparse.ArgumentParser(prog="tiny_llm_b200.cli")
     sub = ap.add_subparsers(dest="command", required=True)
     for name, fn in (("generate", cmd_generate), ("batch", cmd_batch)):
         p = sub.add_parser(name)
         p.set_defaults(fn=fn)
         p.add_argument("--model", default=None, help="checkpoint directory (config.json + *.safetensors [+ tokenizer files])")
-        p.add_argument("--synthetic", default=None, help="random weights of a named shape (tiny, tiny-d128, qwen3-0.6b, qwen3-4b) instead of --model")
+        p.add_argument("--synthetic", default=None, help="random weights of a named shape (tiny, tiny-d128, qwen3-0.6b, qwen3-4b, voluzen[:LAYERS]) instead of --model")
         p.add_argument("--prompt", default="Give me a short introduction to large language models.")
         p.add_argument("--prompt-ids", default=None, help="comma-separated token ids (';' between requests for `batch`)")
         p.add_argument("--loader", choices=["week2", "week3"], default="week3")
         p.add_argument("--device", default="cuda:0")
+        p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16", help="compute dtype of designs with unquantised weights")
         p.add_argument("--disable-paged-attention", action="store_true")
         p.add_argument("--enable-thinking", action="store_true")
         p.add_argument("--max-new-tokens", type=int, default=128)

@@ -184,3 +184,88 @@ def weight_stream_bytes(args) -> int:
     per_layer = args.hidden_size * (q_width + 2 * kv_width) + q_width * args.hidden_size + 3 * args.hidden_size * args.intermediate_size
     weights = args.num_hidden_layers * per_layer + args.vocab_size * args.hidden_size
     return weights * 17 // 32
+
+
+# ---- Voluzen (latent attention + mixture of experts; voluzen.py) -------------------------------------------
+def voluzen_config(*, width=128, vocab=256, pattern="WCSM", heads=2, dim=16, rot_dim=8, vdim=16, kv_rank=32, window=24,
+                   ff=96, experts=6, top=2, expert_ff=32, shared_ff=48, eps=1e-5, base=10000.0) -> dict:
+    """A config.json for a stack spelled by ``pattern``, one letter a layer: ``W`` sliding-window latent attention
+    with a dense feed-forward, ``w`` the same with experts, ``C`` causal latent attention with experts, ``c`` causal
+    with a dense feed-forward, ``S`` causal reading the cache of the nearest caching causal layer before it (experts),
+    ``M`` causal with experts and no shared expert, ``N`` causal with no feed-forward at all."""
+    layers, last_causal = [], None
+    for i, letter in enumerate(pattern):
+        windowed = letter in "Ww"
+        mixer = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "scale": float((dim + rot_dim) ** -0.5),
+                 "rot": {"base": float(base) * (2 if windowed else 1), "dims": rot_dim}}
+        if windowed:
+            mixer["mask"] = {"size": window}
+        if letter == "S":
+            if last_causal is None:
+                raise ValueError("'S' needs a caching causal layer before it")
+            mixer["kv_from"] = last_causal
+        elif not windowed:
+            last_causal = i
+        if letter in "Wc":
+            mlp = {"kind": "dense", "ff": ff}
+        elif letter == "N":
+            mlp = None
+        else:
+            mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff}}
+            if letter != "M" and shared_ff:
+                mlp["shared"] = {"ff": shared_ff}
+        layers.append({"type": "latent_attention_2" if windowed else "latent_attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Voluzen", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+
+
+def synthetic_voluzen(config: dict, seed: int = 0, dtype=torch.bfloat16) -> dict:
+    """Random tensors for ``config`` under the checkpoint's names (CPU, seeded)."""
+    gen = torch.Generator().manual_seed(seed)
+    D = config["width"]
+
+    def mat(out_dim, in_dim, gain=1.0):
+        return (torch.randn(out_dim, in_dim, generator=gen) * (gain / in_dim**0.5)).to(dtype)
+
+    def vec(n, centre, spread):
+        return (centre + spread * torch.randn(n, generator=gen)).to(dtype)
+
+    tensors = {"embed": (torch.randn(config["vocab"], D, generator=gen)).to(dtype), "final.norm": vec(D, 0.0, 0.1), "head": mat(config["vocab"], D)}
+    for i, layer in enumerate(config["layers"]):
+        m, p = layer["mixer"], f"l{i}."
+        H, dn, dr, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+        tensors[p + "mix.q"] = mat(H * (dn + dr), D)
+        if m.get("kv_from") is None:
+            tensors[p + "mix.dkv"] = mat(R + dr, D, 2.0)
+            tensors[p + "mix.dkv.norm"] = vec(R, 1.0, 0.1)
+        tensors[p + "mix.uk"] = mat(H * dn, R)
+        tensors[p + "mix.uv"] = mat(H * dv, R)
+        tensors[p + "mix.o"] = mat(D, H * dv)
+        tensors[p + "norm1"], tensors[p + "ls1"] = vec(D, 0.0, 0.1), vec(D, 0.7, 0.2)
+        mlp = layer.get("mlp")
+        if not mlp:
+            continue
+        tensors[p + "norm2"], tensors[p + "ls2"] = vec(D, 0.0, 0.1), vec(D, 0.7, 0.2)
+        if mlp["kind"] == "dense":
+            groups = [("mlp.", mlp["ff"])]
+        else:
+            tensors[p + "mlp.router"] = mat(mlp["router"]["experts"], D, 2.0)
+            tensors[p + "mlp.router.b"] = vec(mlp["router"]["experts"], 0.0, 0.3)
+            groups = [(f"mlp.e{k}.", mlp["expert"]["ff"]) for k in range(mlp["router"]["experts"])]
+            if mlp.get("shared"):
+                groups.append(("mlp.shared.", mlp["shared"]["ff"]))
+        for q, ff in groups:
+            tensors[p + q + "gate"], tensors[p + q + "up"], tensors[p + q + "down"] = mat(ff, D, 2.0), mat(ff, D), mat(D, ff)
+    return tensors
+
+
+def save_voluzen(config: dict, tensors: dict, path) -> None:
+    """Write ``config.json`` + ``model.safetensors`` (a directory ``load_model`` reads)."""
+    import json
+    from pathlib import Path
+
+    from safetensors.torch import save_file
+
+    path = Path(path)
+    path.mkdir(parents=True, exist_ok=True)
+    (path / "config.json").write_text(json.dumps(config, indent=1))
+    save_file({k: v.contiguous() for k, v in tensors.items()}, str(path / "model.safetensors"))
