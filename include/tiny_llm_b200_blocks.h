@@ -65,6 +65,16 @@ int tlb_latent_attention(const void *q_lat, long long ql_token, long long ql_hea
                          const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles, const int32_t *tok_pos,
                          int heads, int window, float scale, void *out, long long o_token, long long o_head, int dtype, void *stream);
 
+/* The same on the tensor cores, for the bf16 cache: 32 query rows per CTA = tile_tokens consecutive tokens x min(heads, 32)
+ * heads, with tile_tokens = tlb_latent_attention_mma_tile_tokens(heads) the most tokens a tile may hold.  Needs
+ * rank <= 512, (rank + rot) % 8 == 0, page_size % 32 == 0 (tlb_latent_attention_mma_supported). */
+int tlb_latent_attention_mma_tile_tokens(int heads);
+int tlb_latent_attention_mma_supported(int rank, int rot, int page_size);
+int tlb_latent_attention_mma(const void *q_lat, long long ql_token, long long ql_head, const void *q_rot, long long qr_token,
+                             long long qr_head, const void *slab, int num_pages, int page_size, int rank, int rot,
+                             const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles, const int32_t *tok_pos,
+                             int heads, int window, float scale, void *out, long long o_token, long long o_head, void *stream);
+
 /* out[t, j] = act(gu[t, j]) * gu[t, width + j]; act 0 = silu, 1 = gelu (tanh form). */
 int tlb_gated_act(const void *gu, void *out, int rows, int width, int act, int dtype, void *stream);
 

@@ -37,16 +37,22 @@ def row_error(got, want):
 
 
 def rows_match(got, want, dtype):
-    """float32: every row within TOL.  bfloat16: random routers have close calls that 8-bit mantissas decide the
-    other way for a few tokens (those rows then differ by much more than rounding), so the bound is on the typical
-    row and on how many rows may stray; the float32 run of the same schedule is the sharp test of the logic."""
-    d = (got.double().cpu() - want.double())
-    d = d - d.mean(-1, keepdim=True)
-    w = want.double() - want.double().mean(-1, keepdim=True)
-    err = d.pow(2).mean(-1).sqrt() / w.pow(2).mean(-1).sqrt().clamp_min(1e-9)
-    if dtype == torch.float32:
-        return err.max().item() < TOL[dtype]
-    return err.median().item() < 2e-2 and (err > 1e-1).double().mean().item() <= 0.25
+    return row_error(got, want) < TOL[dtype]
+
+
+def decisive_routers(tensors):
+    """For runs in bfloat16: a random router has close calls that an 8-bit mantissa decides the other way for a few
+    tokens, and such a row then differs by far more than rounding.  Here the bias separates the experts by a wide
+    margin (the chosen set is fixed, the weights among the chosen still follow the token), so every row can be held
+    to the rounding bound.  The float32 runs keep the random routers, with choices that change from token to token."""
+    out = dict(tensors)
+    for name, t in tensors.items():
+        if name.endswith(".router"):
+            out[name] = (0.05 * t.float()).to(t.dtype)
+        elif name.endswith(".router.b"):
+            order = torch.randperm(t.numel(), generator=torch.Generator().manual_seed(t.numel()))
+            out[name] = order.to(torch.float32).to(t.dtype)
+    return out
 
 
 def close(got, want, tol):
@@ -115,8 +121,13 @@ def build_cache(dev, dtype, rows, page_size, page_order):
     return slab.to(dev), table.to(dev)
 
 
-def run_attention(dev, dtype, q_full, rows, positions, rank, window, scale, page_size=32):
+def run_attention(dev, dtype, q_full, rows, positions, rank, window, scale, page_size=32, kernel=None):
     S = rows.shape[0]
+    chosen, tile_tokens = blocks.attention_kernel(dtype, q_full.shape[1], rank, rows.shape[1] - rank, page_size)
+    if kernel == "general":
+        chosen, tile_tokens = "general", blocks.ATTENTION_TILE_TOKENS
+    elif kernel is not None:
+        assert chosen == kernel, "these sizes should go to the tensor-core kernel"
     order = list(reversed(range(-(-S // page_size))))
     slab, table = build_cache(dev, dtype, rows, page_size, order)
     T, H, width = q_full.shape
@@ -125,12 +136,12 @@ def run_attention(dev, dtype, q_full, rows, positions, rank, window, scale, page
     tiles, first = [], 0
     while first < T:  # runs of consecutive positions, at most 4 long
         n = 1
-        while first + n < T and n < blocks.ATTENTION_TILE_TOKENS and positions[first + n] == positions[first + n - 1] + 1:
+        while first + n < T and n < tile_tokens and positions[first + n] == positions[first + n - 1] + 1:
             n += 1
         tiles.append((first, n, 0))
         first += n
     blocks.latent_attention(q[:, :, :rank], q[:, :, rank:], slab, table, torch.tensor(tiles, dtype=torch.int32, device=dev),
-                            positions.to(torch.int32).to(dev), window=window, scale=scale, out=out.transpose(0, 1))
+                            positions.to(torch.int32).to(dev), window=window, scale=scale, out=out.transpose(0, 1), kernel=chosen)
     return out.transpose(0, 1)
 
 
@@ -148,6 +159,20 @@ def test_latent_attention_against_plain_attention(dev, dtype, rank, rot, heads):
         close(got, want, 2e-6 if dtype == torch.float32 else 1.5e-2)
 
 
+@pytest.mark.parametrize("rank,rot,heads", [(32, 8, 1), (96, 16, 4), (130, 6, 5), (64, 32, 16), (256, 64, 40), (512, 64, 3)])
+def test_tensor_core_attention_against_plain_attention_and_the_general_kernel(dev, rank, rot, heads):
+    g = torch.Generator().manual_seed(rank + heads)
+    S = 200
+    rows = torch.randn(S, rank + rot, generator=g).to(torch.bfloat16)
+    positions = torch.tensor(list(range(0, 9)) + [30, 31, 32, 33, 34, 63, 64, 65] + list(range(120, 150)) + [199])
+    q = torch.randn(len(positions), heads, rank + rot, generator=g).to(torch.bfloat16)
+    for window in (0, 1, 33, 64):
+        want = O.cache_attention(q.double(), rows.double(), positions, rank, window, 0.09)
+        got = run_attention(dev, torch.bfloat16, q, rows, positions, rank, window, 0.09, kernel="mma")
+        close(got, want, 1.5e-2)
+        close(got, run_attention(dev, torch.bfloat16, q, rows, positions, rank, window, 0.09, kernel="general").double().cpu(), 1.5e-2)
+
+
 @pytest.mark.parametrize("window", [0, 48])
 def test_one_key_that_matters_far_away_at_page_borders_and_window_edges(dev, window):
     """Key j* carries all the weight when visible (its row is aligned with the query and scaled up) and a value unlike
@@ -163,13 +188,14 @@ def test_one_key_that_matters_far_away_at_page_borders_and_window_edges(dev, win
         wanted = [star, star + window - 1, star + window, S - 1] if window else [star, (star + S) // 2, S - 1]
         positions = torch.unique(torch.tensor([min(S - 1, p) for p in wanted]))
         q = (30.0 * direction).repeat(len(positions), 2, 1)
-        got = run_attention(dev, torch.float32, q, rows, positions, rank, window, 1.0, page).cpu()
         want = O.cache_attention(q.double(), rows.double(), positions, rank, window, 1.0)
-        close(got, want, 1e-5)
-        for r, p in enumerate(positions.tolist()):
-            sees = star <= p and (not window or p - star < window)
-            share = float(got[r, 0] @ rows[star, :rank] / rows[star, :rank].pow(2).sum())
-            assert (share > 0.99) if sees else (abs(share) < 0.01), (star, p, share)
+        for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):  # the general kernel, then the tensor-core one
+            got = run_attention(dev, dtype, q, rows, positions, rank, window, 1.0, page).float().cpu()
+            close(got, want, tol)
+            for r, p in enumerate(positions.tolist()):
+                sees = star <= p and (not window or p - star < window)
+                share = float(got[r, 0] @ rows[star, :rank] / rows[star, :rank].pow(2).sum())
+                assert (share > 0.98) if sees else (abs(share) < 0.02), (star, p, share, dtype)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -238,6 +264,8 @@ def model_and_oracle(dev, name, dtype, max_tokens=None):
     if key not in _models:
         config = voluzen_config(**CONFIGS[name])
         tensors = synthetic_voluzen(config, seed=len(name))
+        if dtype == torch.bfloat16:
+            tensors = decisive_routers(tensors)
         model = model_class("Voluzen").from_checkpoint(config, tensors, dtype=dtype, device=dev, max_tokens=max_tokens)
         _models[key] = (model, config, tensors)
     return _models[key]
@@ -282,7 +310,7 @@ def test_layers_one_by_one(dev, name):
     from tiny_llm_b200.ragged import RaggedPlan
 
     cache = model.create_kv_cache()
-    plan = RaggedPlan([RaggedEntry(prompt, cache)], dev, blocks.ATTENTION_TILE_TOKENS)
+    plan = RaggedPlan([RaggedEntry(prompt, cache)], dev, model.tile_sizes)
     x32, h = blocks.embed_rows(plan.ids, model.embed)
     for i, layer in enumerate(model.layers):
         h = layer.norm1(layer.mixer(h, plan, model.page_pool.slabs[layer.slab_index]), residual=x32)
@@ -365,6 +393,8 @@ def test_greedy_generation_through_the_entry_points(dev, dtype, tmp_path):
     model's greedy tokens; the checkpoint goes through a directory and load_model."""
     config = voluzen_config(**CONFIGS["mixed"])
     tensors = synthetic_voluzen(config, seed=21)
+    if dtype == torch.bfloat16:
+        tensors = decisive_routers(tensors)
     save_voluzen(config, tensors, tmp_path / "ckpt")
     model = load_model(tmp_path / "ckpt", device=dev, dtype=dtype, max_tokens=6 * 64)
     prompts = [ids_for(n, 160, 30 + n) for n in (5, 70, 2, 33, 64)]

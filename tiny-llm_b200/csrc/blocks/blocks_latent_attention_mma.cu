@@ -1,0 +1,257 @@
+// Latent attention on the tensor cores (bf16 cache, mma.sync m16n8k16, fp32 accumulation and softmax).
+//
+// All heads of a token attend the same keys (cache row j = [latent | rotated shared key part]) and mix the same values
+// (the latent part of the row), so a CTA takes 32 query rows = a run of consecutive tokens of one sequence x a group of
+// heads and streams every 32-key tile of the paged cache through shared memory ONCE for all of them (cp.async into a
+// second buffer while the current one is used).  Per key tile, with 8 warps:
+//   1. scores:  the 32 x 32 block S = Q K^T is 2 x 4 blocks of 16 x 8, one per warp, over the full key width;
+//   2. softmax: each warp owns 4 rows (lane = key): mask, running maximum / sum, P = exp(S - m) as bf16, rescale factor;
+//   3. values:  O[32 x rank] += P V, warp = (16-row half, quarter of the value columns); V is the key tile itself.
+// A row's arithmetic depends only on its own position (32-aligned key tiles in ascending order): what else is in the
+// CTA, the launch or the batch does not change its result.
+#include "blocks_common.cuh"
+
+namespace tlb {
+
+constexpr int kMRows = 32;   // query rows per CTA
+constexpr int kMKeys = 32;   // keys per tile
+constexpr int kMWarps = 8;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3, const void *p) {
+    uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t &r0, uint32_t &r1, const void *p) {
+    uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3, const void *p) {
+    uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void *dst, const void *src) {
+    uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// PAIRS = pairs of 8-column value tiles per warp (the warp's quarter of the value columns = 16 * PAIRS columns).
+template <int PAIRS>
+__global__ void __launch_bounds__(kMWarps * 32)
+latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, long long ql_head, const bf16 *__restrict__ q_rot, long long qr_token,
+                            long long qr_head, const bf16 *__restrict__ slab, int num_pages, int page_size, int rank, int rot,
+                            const int32_t *__restrict__ block_table, int max_pages, const int32_t *__restrict__ tiles,
+                            const int32_t *__restrict__ tok_pos, int heads, int head_group, int window, float scale, bf16 *__restrict__ out,
+                            long long o_token, long long o_head, int row_stride /* shared-memory row stride in elements */) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int width = rank + rot;
+    bf16 *sq = reinterpret_cast<bf16 *>(smem_raw);                  // [32][row_stride]
+    bf16 *sk0 = sq + kMRows * row_stride;                           // 2 x [32][row_stride]
+    bf16 *sp = sk0 + 2 * kMKeys * row_stride;                       // [32][40]
+    float *ss = reinterpret_cast<float *>(sp + kMRows * 40);        // [32][33]
+    float *s_alpha = ss + kMRows * 33;                              // [32]
+    float *s_l = s_alpha + kMRows;                                  // [32]
+
+    const int first = tiles[blockIdx.x * 3 + 0], count = tiles[blockIdx.x * 3 + 1], seq = tiles[blockIdx.x * 3 + 2];
+    const int head0 = blockIdx.y * head_group;
+    const int nheads = min(head_group, heads - head0);
+    const int pos0 = tok_pos[first];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int chunks = width / 8;  // 16-byte pieces of a cache row
+
+    // zero everything once: padding columns of Q and K must read as zero in every product
+    for (int i = threadIdx.x; i < (3 * kMRows * row_stride) / 8; i += blockDim.x) reinterpret_cast<uint4 *>(sq)[i] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+    // queries: row = token-in-tile * head_group + head-in-group
+    for (int r = warp; r < kMRows; r += kMWarps) {
+        int tq = r / head_group, hh = r % head_group;
+        if (tq >= count || hh >= nheads) continue;
+        const bf16 *ql = q_lat + (size_t)(first + tq) * ql_token + (size_t)(head0 + hh) * ql_head;
+        const bf16 *qr = q_rot + (size_t)(first + tq) * qr_token + (size_t)(head0 + hh) * qr_head;
+        for (int d = lane; d < width; d += 32) sq[r * row_stride + d] = d < rank ? ql[d] : qr[d - rank];
+    }
+
+    const int hi = pos0 + count - 1;
+    int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+    lo = lo / kMKeys * kMKeys;
+    const int32_t *table = block_table + (size_t)seq * max_pages;
+    const int n_tiles = (hi - lo) / kMKeys + 1;
+
+    auto stage = [&](int tile, bf16 *dst) {
+        int k0 = lo + tile * kMKeys;
+        int page = table[k0 / page_size];
+        bool ok = page >= 0 && page < num_pages;
+        int valid = ok ? min(kMKeys, hi - k0 + 1) : 0;
+        const bf16 *src = slab + ((size_t)(ok ? page : 0) * page_size + (k0 % page_size)) * width;
+        for (int c = threadIdx.x; c < kMKeys * chunks; c += blockDim.x) {
+            int j = c / chunks, piece = c - j * chunks;
+            bf16 *d = dst + j * row_stride + piece * 8;
+            if (j < valid) cp_async16(d, src + (size_t)j * width + piece * 8);
+            else *reinterpret_cast<uint4 *>(d) = make_uint4(0, 0, 0, 0);
+        }
+        cp_async_commit();
+    };
+
+    // softmax state of the 4 rows this warp owns (uniform over the lanes)
+    float m_run[4], l_run[4];
+    int row_pos[4];
+    bool row_live[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int r = warp * 4 + i, tq = r / head_group, hh = r % head_group;
+        m_run[i] = -INFINITY, l_run[i] = 0.f;
+        row_live[i] = tq < count && hh < nheads;
+        row_pos[i] = pos0 + tq;
+    }
+    const int mt = warp & 1, nt = warp >> 1;          // score block of this warp; nt is also its quarter of the value columns
+    float acc[2 * PAIRS][4];
+#pragma unroll
+    for (int i = 0; i < 2 * PAIRS; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+    stage(0, sk0);
+    const int ksteps = (width + 15) / 16;
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        bf16 *sk = sk0 + (tile & 1) * kMKeys * row_stride;
+        cp_async_wait<0>();
+        __syncthreads();  // this tile (and, first time, the queries) are in shared memory; every warp is done with the previous tile
+        if (tile + 1 < n_tiles) stage(tile + 1, sk0 + ((tile + 1) & 1) * kMKeys * row_stride);  // lands while this tile is computed
+
+        // 1. scores
+        {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const bf16 *qa = sq + (mt * 16 + (lane & 15)) * row_stride + (lane >> 4) * 8;
+            const bf16 *kb = sk + (nt * 8 + (lane & 7)) * row_stride + ((lane >> 3) & 1) * 8;
+            for (int ks = 0; ks < ksteps; ++ks) {
+                uint32_t a0, a1, a2, a3, b0, b1;
+                ldmatrix_x4(a0, a1, a2, a3, qa + ks * 16);
+                ldmatrix_x2(b0, b1, kb + ks * 16);
+                mma_bf16(c, a0, a1, a2, a3, b0, b1);
+            }
+            int g = lane >> 2, t = lane & 3;
+            float *o = ss + (mt * 16 + g) * 33 + nt * 8 + 2 * t;
+            o[0] = c[0] * scale, o[1] = c[1] * scale;
+            o[8 * 33] = c[2] * scale, o[8 * 33 + 1] = c[3] * scale;
+        }
+        __syncthreads();
+
+        // 2. softmax over this tile's keys, 4 rows per warp
+        {
+            const int key = lo + tile * kMKeys + lane;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                int r = warp * 4 + i;
+                bool vis = row_live[i] && key <= row_pos[i] && (window <= 0 || row_pos[i] - key < window);
+                float s = vis ? ss[r * 33 + lane] : -INFINITY;
+                float m_new = fmaxf(m_run[i], warp_max(s));
+                float alpha = m_new == -INFINITY ? 1.f : expf(m_run[i] - m_new);
+                float p = vis ? expf(s - m_new) : 0.f;
+                bf16 pb = __float2bfloat16_rn(p);
+                // the sum uses the rounded probability, so numerator and denominator see the same weights
+                l_run[i] = l_run[i] * alpha + warp_sum(__bfloat162float(pb));
+                m_run[i] = m_new;
+                sp[r * 40 + lane] = pb;
+                if (lane == 0) s_alpha[r] = alpha;
+            }
+        }
+        __syncthreads();
+
+        // 3. values
+        {
+            int g = lane >> 2;
+            float a_lo = s_alpha[mt * 16 + g], a_hi = s_alpha[mt * 16 + g + 8];
+#pragma unroll
+            for (int i = 0; i < 2 * PAIRS; ++i) acc[i][0] *= a_lo, acc[i][1] *= a_lo, acc[i][2] *= a_hi, acc[i][3] *= a_hi;
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+                uint32_t a0, a1, a2, a3;
+                ldmatrix_x4(a0, a1, a2, a3, sp + (mt * 16 + (lane & 15)) * 40 + kk * 16 + (lane >> 4) * 8);
+                const bf16 *vb = sk + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * row_stride + nt * (16 * PAIRS) + (lane >> 4) * 8;
+#pragma unroll
+                for (int pr = 0; pr < PAIRS; ++pr) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(b0, b1, b2, b3, vb + pr * 16);
+                    mma_bf16(acc[2 * pr], a0, a1, a2, a3, b0, b1);
+                    mma_bf16(acc[2 * pr + 1], a0, a1, a2, a3, b2, b3);
+                }
+            }
+        }
+    }
+
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        if (lane == 0) s_l[warp * 4 + i] = l_run[i];
+    __syncthreads();
+    {
+        int g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            int r = mt * 16 + g + half * 8, tq = r / head_group, hh = r % head_group;
+            if (tq >= count || hh >= nheads) continue;
+            float inv = 1.0f / s_l[r];
+            bf16 *o = out + (size_t)(first + tq) * o_token + (size_t)(head0 + hh) * o_head;
+#pragma unroll
+            for (int i = 0; i < 2 * PAIRS; ++i) {
+                int col = nt * (16 * PAIRS) + i * 8 + 2 * t;
+                if (col < rank) o[col] = __float2bfloat16_rn(acc[i][half * 2] * inv);
+                if (col + 1 < rank) o[col + 1] = __float2bfloat16_rn(acc[i][half * 2 + 1] * inv);
+            }
+        }
+    }
+}
+
+}  // namespace tlb
+
+using namespace tlb;
+
+// Rows of a CTA: `tile_tokens` consecutive tokens x `head_group` heads, head_group = min(heads, 32), tile_tokens = 32 / head_group.
+extern "C" int tlb_latent_attention_mma_tile_tokens(int heads) { return heads >= kMRows ? 1 : kMRows / heads; }
+
+extern "C" int tlb_latent_attention_mma_supported(int rank, int rot, int page_size) {
+    return rank > 0 && rank <= 512 && (rank + rot) % 8 == 0 && page_size % kMKeys == 0;
+}
+
+extern "C" int tlb_latent_attention_mma(const void *q_lat, long long ql_token, long long ql_head, const void *q_rot, long long qr_token,
+                                        long long qr_head, const void *slab, int num_pages, int page_size, int rank, int rot,
+                                        const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles, const int32_t *tok_pos,
+                                        int heads, int window, float scale, void *out, long long o_token, long long o_head, void *stream) {
+    if (num_tiles <= 0) return TL_OK;
+    if (!q_lat || (!q_rot && rot > 0) || !slab || !block_table || !tiles || !tok_pos || !out || heads <= 0 || max_pages <= 0 || num_pages <= 0)
+        return tl::fail(TL_EINVAL, "latent_attention_mma: bad argument");
+    if (!tlb_latent_attention_mma_supported(rank, rot, page_size))
+        return tl::fail(TL_EINVAL, "latent_attention_mma: rank <= 512, (rank + rot) %% 8 == 0 and page_size %% 32 == 0 are required");
+    if (!tl::aligned16(slab)) return tl::fail(TL_EINVAL, "latent_attention_mma: the cache must be 16-byte aligned");
+    int width = rank + rot;
+    int pairs = ceil_div(ceil_div(rank, 8), 8);            // value tiles (8 columns) -> pairs per quarter
+    pairs = pairs <= 1 ? 1 : pairs <= 2 ? 2 : pairs <= 4 ? 4 : 8;
+    int span = max(ceil_div(width, 16) * 16, 64 * pairs);  // columns a row must hold: the padded key width, the four value quarters
+    int row_stride = span + 8;                              // (stride / 8) odd: conflict-free ldmatrix rows
+    size_t smem = (size_t)3 * kMRows * row_stride * 2 + kMRows * 40 * 2 + (size_t)kMRows * 33 * 4 + 2 * kMRows * 4;
+    int head_group = heads >= kMRows ? kMRows : heads;
+    dim3 grid(num_tiles, ceil_div(heads, head_group));
+    cudaStream_t st = as_stream(stream);
+#define TLB_LAM(P)                                                                                                                          \
+    do {                                                                                                                                    \
+        auto kernel = latent_attention_mma_kernel<P>;                                                                                       \
+        if (smem > 48 * 1024) {                                                                                                             \
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                           \
+            if (e != cudaSuccess) return tl::fail(TL_ECUDA, "latent_attention_mma: %s", cudaGetErrorString(e));                             \
+        }                                                                                                                                   \
+        kernel<<<grid, kMWarps * 32, smem, st>>>((const bf16 *)q_lat, ql_token, ql_head, (const bf16 *)(q_rot ? q_rot : q_lat), qr_token,   \
+                                                 qr_head, (const bf16 *)slab, num_pages, page_size, rank, rot, block_table, max_pages, tiles, \
+                                                 tok_pos, heads, head_group, window, scale, (bf16 *)out, o_token, o_head, row_stride);      \
+    } while (0)
+    if (pairs == 1) TLB_LAM(1);
+    else if (pairs == 2) TLB_LAM(2);
+    else if (pairs == 4) TLB_LAM(4);
+    else TLB_LAM(8);
+#undef TLB_LAM
+    TL_LAUNCH_CHECK("latent_attention_mma");
+    return TL_OK;
+}

@@ -44,6 +44,7 @@ BLOCKS_LIB = OUT_DIR / f"libtiny_llm_b200_blocks{SUFFIX}.so"
 BLOCKS_SOURCES = [
     "blocks/blocks_rows.cu",
     "blocks/blocks_latent_attention.cu",
+    "blocks/blocks_latent_attention_mma.cu",
     "blocks/blocks_moe.cu",
 ]
 

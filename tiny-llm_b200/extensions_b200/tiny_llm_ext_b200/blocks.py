@@ -29,6 +29,9 @@ _SIGNATURES = {
     "tlb_rope_rows": (_I, [_VP, _LL, _LL, _I, _I, _I, _I, _D, _VP, _I, _I, _VP]),
     "tlb_latent_append": (_I, [_VP, _VP, _F, _I, _I, _I, _I, _D, _VP, _VP, _VP, _I, _I, _I, _VP, _I, _I, _VP]),
     "tlb_latent_attention": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _VP, _LL, _LL, _I, _VP]),
+    "tlb_latent_attention_mma_tile_tokens": (_I, [_I]),
+    "tlb_latent_attention_mma_supported": (_I, [_I, _I, _I]),
+    "tlb_latent_attention_mma": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _VP, _LL, _LL, _VP]),
     "tlb_gated_act": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
     "tlb_moe_route": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _VP, _VP, _I, _VP]),
     "tlb_moe_max_rows": (_LL, [_I, _I, _I]),
@@ -175,9 +178,19 @@ def latent_append(down, norm_weight, eps, *, rank, rot_dims, interleaved, base, 
                                        _code(down.dtype), _stream(down)))
 
 
-def latent_attention(q_lat, q_rot, slab, block_table, tiles, tok_pos, *, window: int, scale: float, out):
+def attention_kernel(dtype, heads: int, rank: int, rot: int, page_size: int) -> tuple[str, int]:
+    """Which latent-attention kernel serves these sizes, and the most tokens one entry of its ``tiles`` may hold:
+    ``("mma", 32 // min(heads, 32))`` for a bf16 cache the tensor-core kernel can take (32 query rows per CTA), else
+    ``("general", 4)`` (fp32 cache, odd widths; TL_LATENT_MMA=0 forces it)."""
+    if dtype == torch.bfloat16 and _mma_ok(rank, rot, page_size):
+        return "mma", int(library().tlb_latent_attention_mma_tile_tokens(heads))
+    return "general", ATTENTION_TILE_TOKENS
+
+
+def latent_attention(q_lat, q_rot, slab, block_table, tiles, tok_pos, *, window: int, scale: float, out, kernel: str = "general"):
     """``q_lat [T, H, rank]``, ``q_rot [T, H, rot]`` and ``out [T, H, rank]`` are views with arbitrary token / head strides
-    and unit inner stride; ``tiles [n, 3]`` int32 (first token, count, block-table row)."""
+    and unit inner stride; ``tiles [n, 3]`` int32 (first token, count, block-table row) cut for the tile size that
+    ``attention_kernel`` gives beside the kernel's name."""
     _gpu("latent_attention", q_lat, q_rot, slab, block_table, tiles, tok_pos, out)
     _contig("latent_attention", slab, block_table, tiles, tok_pos)
     T, H, rank = q_lat.shape
@@ -187,10 +200,24 @@ def latent_attention(q_lat, q_rot, slab, block_table, tiles, tok_pos, *, window:
         raise RuntimeError("latent_attention: query / output shapes do not match the cache")
     if not (q_lat.dtype == q_rot.dtype == slab.dtype == out.dtype):
         raise RuntimeError("latent_attention: one dtype for queries, cache and output")
-    _check(library().tlb_latent_attention(_ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(slab), P,
-                                          page_size, rank, rot, _ptr(block_table), block_table.shape[1], _ptr(tiles), tiles.shape[0], _ptr(tok_pos),
-                                          H, int(window or 0), float(scale), _ptr(out), out.stride(0), out.stride(1), _code(slab.dtype), _stream(slab)))
+    lib = library()
+    if kernel == "mma":
+        if slab.dtype != torch.bfloat16:
+            raise RuntimeError("latent_attention: the tensor-core kernel takes a bfloat16 cache")
+        _check(lib.tlb_latent_attention_mma(_ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(slab), P,
+                                            page_size, rank, rot, _ptr(block_table), block_table.shape[1], _ptr(tiles), tiles.shape[0], _ptr(tok_pos),
+                                            H, int(window or 0), float(scale), _ptr(out), out.stride(0), out.stride(1), _stream(slab)))
+        return out
+    if kernel != "general":
+        raise RuntimeError(f"latent_attention: unknown kernel {kernel!r}")
+    _check(lib.tlb_latent_attention(_ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(slab), P,
+                                    page_size, rank, rot, _ptr(block_table), block_table.shape[1], _ptr(tiles), tiles.shape[0], _ptr(tok_pos),
+                                    H, int(window or 0), float(scale), _ptr(out), out.stride(0), out.stride(1), _code(slab.dtype), _stream(slab)))
     return out
+
+
+def _mma_ok(rank: int, rot: int, page_size: int) -> bool:
+    return os.environ.get("TL_LATENT_MMA", "1") != "0" and bool(library().tlb_latent_attention_mma_supported(rank, rot, page_size))
 
 
 def gated_act(gate_up: torch.Tensor, act: int) -> torch.Tensor:

@@ -44,6 +44,12 @@ class LatentAttention:
     def cache_width(self) -> int:
         return self.rank + self.rot_dim
 
+    def attention_kernel(self, slab: torch.Tensor) -> tuple[str, int]:
+        """(kernel name, tokens per work-list entry) for this layer on ``slab [P, page_size, rank + rot]``."""
+        from extensions_b200.tiny_llm_ext_b200 import blocks
+
+        return blocks.attention_kernel(slab.dtype, self.heads, self.rank, self.rot_dim, slab.shape[1])
+
     def __call__(self, h: torch.Tensor, plan, slab: torch.Tensor) -> torch.Tensor:
         from extensions_b200.tiny_llm_ext_b200 import blocks
 
@@ -54,10 +60,11 @@ class LatentAttention:
                                  interleaved=self.interleaved, base=self.rot_base, tok_pos=plan.tok_pos, tok_seq=plan.tok_seq,
                                  block_table=plan.block_table, slab=slab)
         blocks.rope_rows(q, plan.tok_pos, heads=H, head_stride=dn + dr, first=dn, dims=self.rot_dims, base=self.rot_base, interleaved=self.interleaved)
+        kernel, tile_tokens = self.attention_kernel(slab)
         q3 = q.view(T, H, dn + dr)
         q_lat = torch.bmm(q3[:, :, :dn].transpose(0, 1), self.w_uk)          # [H, T, rank]
         o_lat = torch.empty_like(q_lat)
-        blocks.latent_attention(q_lat.transpose(0, 1), q3[:, :, dn:], slab, plan.block_table, plan.tiles, plan.tok_pos,
-                                window=self.window, scale=self.scale, out=o_lat.transpose(0, 1))
+        blocks.latent_attention(q_lat.transpose(0, 1), q3[:, :, dn:], slab, plan.block_table, plan.tiles_for(tile_tokens), plan.tok_pos,
+                                window=self.window, scale=self.scale, out=o_lat.transpose(0, 1), kernel=kernel)
         o = torch.bmm(o_lat, self.w_uv_t)                                     # [H, T, vdim]
         return linear(o.transpose(0, 1).reshape(T, H * self.vdim), self.w_o)

@@ -4,10 +4,11 @@ A continuous-batching step is a flat list of tokens: a portion of one request's 
 others.  ``RaggedEntry`` names one request's share, ``RaggedPlan`` is what the kernels need, built on the host from the
 requests' page lists and moved to the device as ONE pinned block:
 
-    ids [T] | tok_pos [T] | tok_seq [T] | want_rows [W] | tiles [n, 3] | block_table [S, max_pages]
+    ids [T] | tok_pos [T] | tok_seq [T] | want_rows [W] | block_table [S, max_pages] | tiles [n, 3] per tile size
 
 ``tok_pos`` is the position of a token in its sequence, ``tok_seq`` its row in this step's block table, ``tiles`` the
-attention kernel's work list (runs of at most ``tile`` consecutive tokens of one sequence).  Building the plan also
+attention kernels' work lists (runs of at most ``tile`` consecutive tokens of one sequence; one list per tile size
+the model's layers ask for, ``tiles_for(size)``).  Building the plan also
 does the step's cache bookkeeping: every request's page list grows by its new tokens (pages come from the pool's free
 list first), before anything is launched.
 """
@@ -29,7 +30,8 @@ class RaggedEntry:
 
 
 class RaggedPlan:
-    def __init__(self, entries: Sequence[RaggedEntry], device, tile: int):
+    def __init__(self, entries: Sequence[RaggedEntry], device, tile):
+        sizes = sorted({int(tile)} if isinstance(tile, int) else {int(t) for t in tile})
         owners = []
         for e in entries:
             if len(e.tokens) == 0:
@@ -53,16 +55,20 @@ class RaggedPlan:
         max_pages = max(o.num_pages for o in owners)
         wants = [list(e.want) if e.want is not None else [len(e.tokens) - 1] for e in entries]
         W = sum(len(w) for w in wants)
-        n_tiles = sum(-(-len(e.tokens) // tile) for e in entries)
-        total = 3 * T + W + 3 * n_tiles + S * max_pages
+        n_tiles = {size: sum(-(-len(e.tokens) // size) for e in entries) for size in sizes}
+        total = 3 * T + W + S * max_pages + 3 * sum(n_tiles.values())
         host = torch.empty(max(total, 1), dtype=torch.int32, pin_memory=torch.cuda.is_available() and torch.device(device).type == "cuda")
         buf = host.numpy()
         ids, pos, seq = buf[0:T], buf[T : 2 * T], buf[2 * T : 3 * T]
         want = buf[3 * T : 3 * T + W]
-        tiles = buf[3 * T + W : 3 * T + W + 3 * n_tiles].reshape(n_tiles, 3)
-        table = buf[3 * T + W + 3 * n_tiles : total].reshape(S, max_pages)
+        table = buf[3 * T + W : 3 * T + W + S * max_pages].reshape(S, max_pages)
         table[:] = -1
-        t = w = k = 0
+        tile_at, at = {}, 3 * T + W + S * max_pages
+        for size in sizes:
+            tile_at[size] = (at, n_tiles[size])
+            at += 3 * n_tiles[size]
+        tile_rows = {size: [] for size in sizes}
+        t = w = 0
         for s, (e, o, start) in enumerate(zip(entries, owners, starts)):
             n = len(e.tokens)
             ids[t : t + n] = np.asarray(e.tokens, dtype=np.int64)
@@ -73,18 +79,25 @@ class RaggedPlan:
                     raise ValueError(f"wanted place {place} is outside the entry's {n} tokens")
                 want[w] = t + place
                 w += 1
-            for first in range(0, n, tile):
-                tiles[k] = (t + first, min(tile, n - first), s)
-                k += 1
+            for size in sizes:
+                tile_rows[size] += [(t + first, min(size, n - first), s) for first in range(0, n, size)]
             table[s, : o.num_pages] = o.page_ids
             t += n
-        self.num_tokens, self.num_seqs, self.num_want, self.num_tiles, self.max_pages = T, S, W, n_tiles, max_pages
+        for size in sizes:
+            start, n = tile_at[size]
+            buf[start : start + 3 * n] = np.asarray(tile_rows[size], dtype=np.int32).reshape(-1)
+        self.num_tokens, self.num_seqs, self.num_want, self.max_pages = T, S, W, max_pages
         self.h2d_bytes = total * 4
         dev = host.to(device, non_blocking=True)
         self._host = host  # keep the pinned block alive until the copy has run
         self.ids, self.tok_pos, self.tok_seq = dev[0:T], dev[T : 2 * T], dev[2 * T : 3 * T]
         self.want_rows = dev[3 * T : 3 * T + W]
-        self.tiles = dev[3 * T + W : 3 * T + W + 3 * n_tiles].view(n_tiles, 3)
-        self.block_table = dev[3 * T + W + 3 * n_tiles : total].view(S, max_pages)
+        self.block_table = dev[3 * T + W : 3 * T + W + S * max_pages].view(S, max_pages)
+        self._tiles = {size: dev[start : start + 3 * n].view(n, 3) for size, (start, n) in tile_at.items()}
+        self.tiles = self._tiles[sizes[0]]
         self.want_counts = [len(x) for x in wants]
         self.starts = starts
+
+    def tiles_for(self, size: int) -> torch.Tensor:
+        """The work list cut into runs of at most ``size`` tokens (one of the sizes the plan was built for)."""
+        return self._tiles[size]

@@ -97,6 +97,8 @@ class VoluzenModel:
         self.head = take("head")
         max_pages = None if max_tokens is None else -(-int(max_tokens) // page_size)
         self.page_pool = LatentPagedPool(widths, page_size=page_size, dtype=dtype, device=self.device, max_pages=max_pages)
+        # the attention work-list granularities the layers use (one list per size in every step's plan)
+        self.tile_sizes = sorted({blocks.attention_kernel(dtype, l.mixer.heads, l.mixer.rank, l.mixer.rot_dim, page_size)[1] for l in self.layers})
 
     @staticmethod
     def _feed_forward(spec, prefix: str, take):
@@ -128,7 +130,7 @@ class VoluzenModel:
     def forward_ragged(self, entries: list[RaggedEntry]) -> torch.Tensor:
         """One step over ``entries`` -> fp32 logits ``[sum of wanted places, vocab]`` in entry order.  Appends the
         entries' tokens to their caches."""
-        plan = RaggedPlan(entries, self.device, blocks.ATTENTION_TILE_TOKENS)
+        plan = RaggedPlan(entries, self.device, self.tile_sizes)
         self.h2d_bytes += plan.h2d_bytes
         return self._forward_plan(plan)
 
