@@ -836,13 +836,189 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------ workload: voluzen (latent attention + experts, beside Qwen3 W4A16 of equal size)
+VOLUZEN_SIZES = {
+    # a few layers at sizes that resemble real models of this kind; the Qwen3 arm has the same width, depth, head count and
+    # the same ACTIVE feed-forward width (top * expert_ff + shared_ff)
+    "w1024": dict(width=1024, vocab=32768, pattern="wCSC", heads=8, dim=64, rot_dim=32, vdim=64, kv_rank=256, window=512,
+                  experts=16, top=2, expert_ff=512, shared_ff=1024, ff=2048),
+    "w2048": dict(width=2048, vocab=32768, pattern="wCSC", heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, window=1024,
+                  experts=64, top=6, expert_ff=1408, shared_ff=2816, ff=11264),
+}
+
+
+def _voluzen_kernels(cfg: dict, device, prompt: int, batch: int, context: int) -> dict:
+    """The design's own kernels alone at this size, CUDA-event timed after warm-up, each against the roofline of its kind
+    (measured cuBLAS bf16 burst for contractions, measured copy bandwidth for streaming kernels).  Inputs exceed L2 where
+    the kernel streams (decode attention, norms); between repetitions a 256 MB buffer is rewritten to flush L2."""
+    from extensions_b200.tiny_llm_ext_b200 import blocks
+
+    peaks = measured_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    bf = torch.bfloat16
+
+    def timed(fn, reps=5):
+        for _ in range(3):
+            fn()
+        best = []
+        for _ in range(reps):
+            flush.fill_(1)
+            best.append(cuda_time_ms(fn))
+        return statistics.median(best)
+
+    H, R, dr, D = cfg["heads"], cfg["kv_rank"], cfg["rot_dim"], cfg["width"]
+    page = 64
+    out = {}
+    kernel, tile = blocks.attention_kernel(bf, H, R, dr, page)
+
+    def attention(tokens_per_seq, seqs, ctx):
+        pages_per = -(-ctx // page)
+        slab = torch.randn((seqs * pages_per, page, R + dr), dtype=torch.float32, device=device).to(bf)
+        table = torch.arange(seqs * pages_per, dtype=torch.int32, device=device).view(seqs, pages_per)
+        T = tokens_per_seq * seqs
+        pos = torch.cat([torch.arange(ctx - tokens_per_seq, ctx, dtype=torch.int32) for _ in range(seqs)]).to(device)
+        tiles = torch.tensor([(s * tokens_per_seq + f, min(tile, tokens_per_seq - f), s) for s in range(seqs) for f in range(0, tokens_per_seq, tile)],
+                             dtype=torch.int32, device=device)
+        q_lat = torch.randn((T, H, R), dtype=torch.float32, device=device).to(bf)
+        q_rot = torch.randn((T, H, dr), dtype=torch.float32, device=device).to(bf)
+        o = torch.empty_like(q_lat)
+        ms = timed(lambda: blocks.latent_attention(q_lat, q_rot, slab, table, tiles, pos, window=0, scale=0.05, out=o, kernel=kernel))
+        return ms, slab.numel() * 2
+
+    ms, _ = attention(prompt, 1, prompt)
+    flops = 2.0 * H * (2 * R + dr) * prompt * (prompt + 1) / 2
+    out["latent_attention_prefill"] = {"kernel": kernel, "tokens": prompt, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
+                                       "of_measured_bf16_burst": round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)}
+    ms, cache_bytes = attention(1, batch, context)
+    out["latent_attention_decode"] = {"kernel": kernel, "batch": batch, "context": context, "ms": round(ms, 4), "gbs": round(cache_bytes / ms / 1e6, 1),
+                                      "of_measured_hbm": round(cache_bytes / ms / 1e6 / peaks["hbm_gbs"], 4)}
+    E, top, ff = cfg["experts"], cfg["top"], cfg["expert_ff"]
+    g = torch.Generator(device="cpu").manual_seed(0)
+    h = torch.randn((prompt, D), generator=g).to(bf).to(device)
+    wg, wu = (torch.randn((E, ff, D), device=device) / D**0.5).to(bf), (torch.randn((E, ff, D), device=device) / D**0.5).to(bf)
+    wd = (torch.randn((E, D, ff), device=device) / ff**0.5).to(bf)
+    router_w, router_b = torch.randn((E, D), device=device).to(bf), torch.zeros(E, device=device).to(bf)
+    idx, gate = blocks.moe_route(h, router_w, router_b, top)
+    ms = timed(lambda: blocks.moe_experts(h, idx, gate, wg, wu, wd, blocks.ACT_SILU))
+    flops = 2.0 * 3 * prompt * top * ff * D
+    out["moe_experts_prefill"] = {"tokens": prompt, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
+                                  "of_measured_bf16_burst": round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)}
+    hb = h[:batch].contiguous()
+    idx, gate = blocks.moe_route(hb, router_w, router_b, top)
+    ms = timed(lambda: blocks.moe_experts(hb, idx, gate, wg, wu, wd, blocks.ACT_SILU))
+    touched = min(E, batch * top) * 3 * ff * D * 2
+    out["moe_experts_decode"] = {"batch": batch, "ms": round(ms, 4), "gbs_upper": round(touched / ms / 1e6, 1),
+                                 "of_measured_hbm_upper": round(touched / ms / 1e6 / peaks["hbm_gbs"], 4)}
+    rows = 65536  # > L2 in fp32
+    y = torch.randn((rows, D), device=device).to(bf)
+    res = torch.randn((rows, D), device=device)
+    w = torch.zeros(D, device=device).to(bf)
+    ms = timed(lambda: blocks.norm_residual(y, w, 1e-5, weight_offset=1.0, scale=w, residual=res))
+    nbytes = rows * D * (2 + 4 + 4 + 2)
+    out["norm_residual"] = {"rows": rows, "ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1), "of_measured_hbm": round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 4)}
+    return out
+
+
+def run_voluzen(args) -> None:
+    """Prefill and decode throughput of the Voluzen design at VOLUZEN_SIZES beside Qwen3 W4A16 (the framework's closest
+    model) of equal width, depth, heads and active feed-forward width; and the design's kernels against their rooflines.
+    One JSON line; random weights, random prompts."""
+    from tiny_llm_b200 import Qwen3ModelWeek3
+    from tiny_llm_b200.batch import greedy_tokens
+    from tiny_llm_b200.kv_cache import BatchingKvCache
+    from tiny_llm_b200.models import model_class
+    from tiny_llm_b200.ragged import RaggedEntry
+    from tiny_llm_b200.synthetic import synthetic_qwen3, synthetic_voluzen, voluzen_config
+
+    device = torch.device("cuda:0")
+    prompt, batch, context, steps = args.prompt_len or 2048, 16, 1024, max(args.steps or 16, 4)
+    sampler = ClockSampler(0)
+    sampler.start()
+    results = []
+    for name, size in VOLUZEN_SIZES.items():
+        config = voluzen_config(**size)
+        model = model_class("Voluzen").from_checkpoint(config, synthetic_voluzen(config, seed=0), device=device, dtype=torch.bfloat16)
+        ids = synthetic_prompt(1, prompt, size["vocab"])
+
+        def prefill_once():
+            cache = model.create_kv_cache()
+            model.forward_ragged([RaggedEntry(ids, cache)])
+            cache[0].release()
+
+        for _ in range(max(args.warmup, 3)):
+            prefill_once()
+        pre_ms = statistics.median(cuda_time_ms(prefill_once) for _ in range(5))
+        caches = [model.create_kv_cache() for _ in range(batch)]
+        for b, cache in enumerate(caches):
+            model.forward_ragged([RaggedEntry(synthetic_prompt(10 + b, context, size["vocab"]), cache)])
+        tokens = [1] * batch
+
+        def decode_step():
+            nonlocal tokens
+            logits = model.forward_ragged([RaggedEntry([t], c) for t, c in zip(tokens, caches)])
+            tokens = greedy_tokens(logits).tolist()  # the device -> host read a serving step makes
+
+        for _ in range(max(args.warmup, 3)):
+            decode_step()
+        torch.cuda.synchronize()
+        dec_ms = cuda_time_ms(lambda: [decode_step() for _ in range(steps)]) / steps
+        for cache in caches:
+            cache[0].release()
+        entry = {"size": name, "config": {k: v for k, v in size.items()}, "prompt_tokens": prompt, "decode_batch": batch, "decode_context": context,
+                 "voluzen": {"prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(prompt / pre_ms * 1e3, 1), "decode_ms_per_step": round(dec_ms, 3),
+                             "decode_tok_s": round(batch / dec_ms * 1e3, 1)}}
+        entry["kernels"] = _voluzen_kernels(size, device, prompt, batch, context)
+        del model, caches
+        torch.cuda.empty_cache()
+
+        # the closest existing model at equal size
+        dims = dict(hidden_size=size["width"], num_hidden_layers=len(size["pattern"]), num_attention_heads=size["heads"],
+                    num_key_value_heads=max(1, size["heads"] // 4), head_dim=128, intermediate_size=size["ff"], vocab_size=size["vocab"])
+        qwen = Qwen3ModelWeek3(synthetic_qwen3(dims, seed=0, device=device), page_size=PAGE_SIZE)
+
+        def q_prefill():
+            cache, _ = _prefill_request(qwen, device, ids)
+            for c in cache:
+                c.release()
+
+        for _ in range(max(args.warmup, 3)):
+            q_prefill()
+        q_pre = statistics.median(cuda_time_ms(q_prefill) for _ in range(5))
+        qwen.decode_graph_max_seq_len = context + 256
+        engine = qwen.decode_engine(batch)
+        tables = [BatchingKvCache(max_active_requests=batch, max_seq_len=context + 256) for _ in range(qwen.num_hidden_layers)]
+        first = []
+        for b in range(batch):
+            cache, logits = _prefill_request(qwen, device, synthetic_prompt(10 + b, context, size["vocab"]))
+            first.append(int(greedy_tokens(logits[:, -1, :])[0]))
+            for layer_cache, table in zip(cache, tables):
+                table.add_request(layer_cache, b)
+        engine.decode_on_device(first, [context] * batch, tables, 4)
+        torch.cuda.synchronize()
+        nxt = engine.next_tokens.tolist()
+        q_dec = cuda_time_ms(lambda: engine.decode_on_device(nxt, [context + 4] * batch, tables, steps)) / steps
+        for table in tables:
+            for b in range(batch):
+                table.remove_request(b)
+        entry["qwen3_w4a16_equal_size"] = {"dims": dims, "prefill_ms": round(q_pre, 3), "prefill_tok_s": round(prompt / q_pre * 1e3, 1),
+                                           "decode_ms_per_step": round(q_dec, 3), "decode_tok_s": round(batch / q_dec * 1e3, 1),
+                                           "note": "decode steps replay a captured graph with token feedback on the device"}
+        del qwen, engine, tables
+        torch.cuda.empty_cache()
+        results.append(entry)
+    clocks = sampler.stop()
+    print(json.dumps({"workload": "voluzen", "metric": "Voluzen prefill / decode tok/s beside Qwen3 W4A16 of equal size", "unit": UNIT, "n_gpus": 1,
+                      "dtype": "bf16 (Voluzen: unquantised weights; Qwen3: 4-bit weights)", "data": "synthetic (random weights, random prompts)",
+                      "steps": steps, "warmup": max(args.warmup, 3), "peaks": measured_peaks(), "clocks": clocks, "sizes": results}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(METRICS), default="decode")
+    ap.add_argument("--workload", choices=sorted(METRICS) + ["voluzen"], default="decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the sweeps / secondary measurements under `extra`")
     ap.add_argument("--requests", type=int, default=0, help="serve/serve8k: total requests over all ranks")
@@ -852,7 +1028,9 @@ def main() -> None:
     args = ap.parse_args()
     if args.steps is None:
         args.steps = {"decode": 128, "prefill": 8}.get(args.workload, 0)
-    if args.impl == "reference":
+    if args.workload == "voluzen":
+        run_voluzen(args)
+    elif args.impl == "reference":
         run_reference(args)
     elif args.workload == "decode":
         run_decode(args)

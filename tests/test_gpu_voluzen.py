@@ -4,7 +4,8 @@ entry points.  Small made-up configurations and random weights; where random wei
 among hundreds, a window's edge) the inputs are built so that one score stands out.
 
 Tolerances: relative root-mean-square error of a logits row (mean taken off) below 5e-5 in float32 mode - every
-product in true fp32, so only summation order differs - and below 3e-2 in bfloat16 mode.
+product in true fp32, so only summation order differs - and below 1e-1 in bfloat16 mode (at widths of 64 to 96 the
+rounding of bf16 activations alone gives 1e-2 typically and up to 6e-2 on single rows; a fault of the logic gives 3e-1 and more).
 """
 
 import math
@@ -21,7 +22,7 @@ from tiny_llm_b200.synthetic import save_voluzen, synthetic_voluzen, voluzen_con
 
 pytestmark = pytest.mark.gpu
 
-TOL = {torch.float32: 5e-5, torch.bfloat16: 3e-2}
+TOL = {torch.float32: 5e-5, torch.bfloat16: 1e-1}
 
 
 @pytest.fixture(scope="module")

@@ -172,6 +172,117 @@ moe_grouped_kernel(const T *__restrict__ a, const T *__restrict__ w1, const T *_
     }
 }
 
+
+// ---- the grouped products on the tensor cores (bf16, K % 8 == 0) ------------------------------------------------
+// One CTA = one 32-row expert tile x 128 output columns; 8 warps = 2 row halves x 4 column quarters of 32, each
+// mma.sync m16n8k16 over 32-wide reduction blocks that cp.async brings into a two-stage ring (A rows gathered
+// through the sorted pair list).  fp32 accumulators; the reduction order of a row is k ascending in both kernels.
+constexpr int kTN = 128, kTK = 32, kTS = kTK + 8;  // row stride 40 elements = 80 B: (80 / 16) odd, conflict-free ldmatrix
+
+__device__ __forceinline__ void moe_ldm_x4(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3, const void *p) {
+    uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void moe_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void moe_cp16(void *dst, const void *src, bool ok) {
+    uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    int bytes = ok ? 16 : 0;  // src-size 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(256)
+moe_grouped_mma_kernel(const bf16 *__restrict__ a, const bf16 *__restrict__ w1, const bf16 *__restrict__ w2, const int32_t *__restrict__ sorted_pair,
+                       const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ counters, int top, int K, int N, int act,
+                       bf16 *__restrict__ inter, float *__restrict__ pair_out) {
+    if ((int)blockIdx.x >= counters[0]) return;
+    __shared__ __align__(16) bf16 sa[2][kTileRows * kTS];
+    __shared__ __align__(16) bf16 sb1[2][kTN * kTS];
+    __shared__ __align__(16) bf16 sb2[GATED ? 2 : 1][GATED ? kTN * kTS : 8];
+    __shared__ int src_row[kTileRows];
+    const int e = tile_expert[blockIdx.x];
+    const int row0 = blockIdx.x * kTileRows, col0 = blockIdx.y * kTN;
+    if (threadIdx.x < kTileRows) {
+        int pair = sorted_pair[row0 + threadIdx.x];
+        src_row[threadIdx.x] = pair < 0 ? -1 : (GATED ? pair / top : row0 + (int)threadIdx.x);
+    }
+    __syncthreads();
+    const bf16 *wa = w1 + (size_t)e * N * K;
+    const bf16 *wb = GATED ? w2 + (size_t)e * N * K : nullptr;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int mt = warp & 1, nq = warp >> 1;
+
+    auto stage = [&](int kb, int buf) {
+        int k0 = kb * kTK;
+        if (threadIdx.x < kTileRows * 4) {  // A: 32 rows x 4 pieces of 8
+            int r = threadIdx.x >> 2, piece = threadIdx.x & 3;
+            int sr = src_row[r], k = k0 + piece * 8;
+            bool ok = sr >= 0 && k < K;
+            moe_cp16(&sa[buf][r * kTS + piece * 8], a + (ok ? (size_t)sr * K + k : 0), ok);
+        }
+        for (int c = threadIdx.x; c < kTN * 4; c += 256) {  // B: 128 rows x 4 pieces
+            int n = c >> 2, piece = c & 3;
+            int k = k0 + piece * 8;
+            bool ok = col0 + n < N && k < K;
+            size_t off = ok ? (size_t)(col0 + n) * K + k : 0;
+            moe_cp16(&sb1[buf][n * kTS + piece * 8], wa + off, ok);
+            if (GATED) moe_cp16(&sb2[buf][n * kTS + piece * 8], wb + off, ok);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    float c1[4][4] = {}, c2[GATED ? 4 : 1][4] = {};
+    const int kblocks = (K + kTK - 1) / kTK;
+    stage(0, 0);
+    for (int kb = 0; kb < kblocks; ++kb) {
+        int buf = kb & 1;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();  // this block has landed; everybody is done with the other buffer
+        if (kb + 1 < kblocks) stage(kb + 1, buf ^ 1);
+#pragma unroll
+        for (int ks = 0; ks < kTK / 16; ++ks) {
+            uint32_t a0, a1, a2, a3;
+            moe_ldm_x4(a0, a1, a2, a3, &sa[buf][(mt * 16 + (lane & 15)) * kTS + ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+            for (int np = 0; np < 2; ++np) {  // two n8 tiles per ldmatrix.x4: rows n..n+7 and n+8..n+15, k halves 0 / 8
+                int n = nq * 32 + np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8;
+                int kk = ks * 16 + ((lane >> 3) & 1) * 8;
+                uint32_t b0, b1, b2, b3;
+                moe_ldm_x4(b0, b1, b2, b3, &sb1[buf][n * kTS + kk]);
+                moe_mma(c1[2 * np], a0, a1, a2, a3, b0, b1);
+                moe_mma(c1[2 * np + 1], a0, a1, a2, a3, b2, b3);
+                if (GATED) {
+                    moe_ldm_x4(b0, b1, b2, b3, &sb2[buf][n * kTS + kk]);
+                    moe_mma(c2[2 * np], a0, a1, a2, a3, b0, b1);
+                    moe_mma(c2[2 * np + 1], a0, a1, a2, a3, b2, b3);
+                }
+            }
+        }
+    }
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        int row = row0 + mt * 16 + g + half * 8;
+        int pair = sorted_pair[row];
+        if (pair < 0) continue;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                int col = col0 + nq * 32 + i * 8 + 2 * t + j;
+                if (col >= N) continue;
+                float v = c1[i][half * 2 + j];
+                if (GATED) inter[(size_t)row * N + col] = __float2bfloat16_rn(moe_act(v, act) * c2[i][half * 2 + j]);
+                else pair_out[(size_t)pair * N + col] = v;
+            }
+        }
+    }
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(const float *__restrict__ pair_out, const float *__restrict__ gate, const T *__restrict__ shared,
                                    float *__restrict__ y, int top, int dim) {
@@ -228,6 +339,13 @@ int tlb_moe_gate_up(const void *h, const void *wg, const void *wu, const int32_t
     if (tokens <= 0) return TL_OK;
     if (!h || !wg || !wu || !sorted_pair || !tile_expert || !counters || !inter || dim <= 0 || ff <= 0 || top <= 0)
         return tl::fail(TL_EINVAL, "moe_gate_up: bad argument");
+    if (dtype == TL_BF16 && dim % 8 == 0 && tl::aligned16(h) && tl::aligned16(wg) && tl::aligned16(wu)) {
+        dim3 tc((unsigned)(tlb_moe_max_rows(tokens, top, experts) / kTileRows), ceil_div(ff, kTN));
+        moe_grouped_mma_kernel<true><<<tc, 256, 0, as_stream(stream)>>>((const bf16 *)h, (const bf16 *)wg, (const bf16 *)wu, sorted_pair, tile_expert,
+                                                                        counters, top, dim, ff, act, (bf16 *)inter, nullptr);
+        TL_LAUNCH_CHECK("moe_gate_up");
+        return TL_OK;
+    }
     dim3 grid((unsigned)(tlb_moe_max_rows(tokens, top, experts) / kTileRows), ceil_div(ff, kBN));
     TLB_DISPATCH(dtype, "moe_gate_up",
                  moe_grouped_kernel<T, true><<<grid, 256, 0, as_stream(stream)>>>((const T *)h, (const T *)wg, (const T *)wu, sorted_pair, tile_expert,
@@ -241,6 +359,13 @@ int tlb_moe_down(const void *inter, const void *wd, const int32_t *sorted_pair, 
     if (tokens <= 0) return TL_OK;
     if (!inter || !wd || !sorted_pair || !tile_expert || !counters || !pair_out || dim <= 0 || ff <= 0 || top <= 0)
         return tl::fail(TL_EINVAL, "moe_down: bad argument");
+    if (dtype == TL_BF16 && ff % 8 == 0 && tl::aligned16(inter) && tl::aligned16(wd)) {
+        dim3 tc((unsigned)(tlb_moe_max_rows(tokens, top, experts) / kTileRows), ceil_div(dim, kTN));
+        moe_grouped_mma_kernel<false><<<tc, 256, 0, as_stream(stream)>>>((const bf16 *)inter, (const bf16 *)wd, nullptr, sorted_pair, tile_expert,
+                                                                         counters, top, ff, dim, 0, nullptr, pair_out);
+        TL_LAUNCH_CHECK("moe_down");
+        return TL_OK;
+    }
     dim3 grid((unsigned)(tlb_moe_max_rows(tokens, top, experts) / kTileRows), ceil_div(dim, kBN));
     TLB_DISPATCH(dtype, "moe_down",
                  moe_grouped_kernel<T, false><<<grid, 256, 0, as_stream(stream)>>>((const T *)inter, (const T *)wd, nullptr, sorted_pair, tile_expert,
