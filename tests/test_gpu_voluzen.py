@@ -5,7 +5,8 @@ among hundreds, a window's edge) the inputs are built so that one score stands o
 
 Tolerances: relative root-mean-square error of a logits row (mean taken off) below 5e-5 in float32 mode - every
 product in true fp32, so only summation order differs - and below 1e-1 in bfloat16 mode (at widths of 64 to 96 the
-rounding of bf16 activations alone gives 1e-2 typically and up to 6e-2 on single rows; a fault of the logic gives 3e-1 and more).
+rounding of bf16 activations alone gives 1e-2 typically and up to 1e-1 on single rows, so whole schedules are held to a
+median of 3e-2 and a worst row of 2e-1; a fault of the logic gives 3e-1 and more, and the float32 run is the sharp test).
 """
 
 import math
@@ -38,7 +39,13 @@ def row_error(got, want):
 
 
 def rows_match(got, want, dtype):
-    return row_error(got, want) < TOL[dtype]
+    if dtype == torch.float32:
+        return row_error(got, want) < TOL[dtype]
+    d = (got.double().cpu() - want.double())
+    d = d - d.mean(-1, keepdim=True)
+    w = want.double() - want.double().mean(-1, keepdim=True)
+    err = d.pow(2).mean(-1).sqrt() / w.pow(2).mean(-1).sqrt().clamp_min(1e-9)
+    return err.median().item() < 3e-2 and err.max().item() < 2 * TOL[dtype]
 
 
 def decisive_routers(tensors):
@@ -169,7 +176,7 @@ def test_tensor_core_attention_against_plain_attention_and_the_general_kernel(de
     q = torch.randn(len(positions), heads, rank + rot, generator=g).to(torch.bfloat16)
     for window in (0, 1, 33, 64):
         want = O.cache_attention(q.double(), rows.double(), positions, rank, window, 0.09)
-        got = run_attention(dev, torch.bfloat16, q, rows, positions, rank, window, 0.09, kernel="mma")
+        got = run_attention(dev, torch.bfloat16, q, rows, positions, rank, window, 0.09, page_size=64, kernel="mma")
         close(got, want, 1.5e-2)
         close(got, run_attention(dev, torch.bfloat16, q, rows, positions, rank, window, 0.09, kernel="general").double().cpu(), 1.5e-2)
 
@@ -178,11 +185,11 @@ def test_tensor_core_attention_against_plain_attention_and_the_general_kernel(de
 def test_one_key_that_matters_far_away_at_page_borders_and_window_edges(dev, window):
     """Key j* carries all the weight when visible (its row is aligned with the query and scaled up) and a value unlike
     any other, so an output either IS that value or has nothing of it."""
-    rank, rot, S, page = 64, 8, 700, 32
+    rank, rot, S, page = 64, 8, 700, 64
     g = torch.Generator().manual_seed(5)
     direction = torch.randn(rank + rot, generator=g)
     direction /= direction.norm()
-    for star in (0, 31, 32, 63, 64, 350, 651, 652, 653, 698, 699):
+    for star in (0, 31, 32, 63, 64, 127, 128, 350, 651, 652, 653, 698, 699):
         rows = 0.05 * torch.randn(S, rank + rot, generator=g)
         rows[star] = 30.0 * direction
         # with a window: the key itself, the last query that still sees it, the first that does not, the newest
@@ -325,10 +332,20 @@ def test_layers_one_by_one(dev, name):
 @pytest.mark.parametrize("name", ["mixed", "equal"])
 def test_prefill_then_token_by_token_decoding_across_windows_and_pages(dev, name, dtype):
     model, config, tensors = model_and_oracle(dev, name, dtype)
-    prompt = ids_for(40 + 120, config["vocab"], 3)  # 120 decoded tokens: the window and two page borders pass by
+    prompt = ids_for(190 + 120, config["vocab"], 3)  # 120 decoded tokens: the window and two page borders pass by
     want = O.forward(config, tensors, prompt)
-    got = run_schedule(model, {"a": prompt}, [[("a", 40)]] + [[("a", 1)]] * 120)["a"]
+    replays = model.graph_replays
+    got = run_schedule(model, {"a": prompt}, [[("a", 190)]] + [[("a", 1)]] * 120)["a"]
     assert rows_match(got, want, dtype)
+    # single-token steps replay a captured graph from their third step on, also across the step at which the block
+    # table outgrows 4 pages (a second graph) - and give what eager steps give
+    assert model.graph_replays - replays >= 110 and model.graph_captures >= 2
+    model.use_decode_graph = False
+    try:
+        eager = run_schedule(model, {"a": prompt}, [[("a", 190)]] + [[("a", 1)]] * 120)["a"]
+    finally:
+        model.use_decode_graph = None
+    assert row_error(eager, got.double()) < (1e-6 if dtype == torch.float32 else 1e-2)
     alone = run_schedule(model, {"a": prompt[:30]}, [[("a", 1)]] * 30)["a"]  # the first tokens, one by one from nothing
     assert rows_match(alone, want[:30], dtype)
 

@@ -2,19 +2,22 @@
 //
 // All heads of a token attend the same keys (cache row j = [latent | rotated shared key part]) and mix the same values
 // (the latent part of the row), so a CTA takes 32 query rows = a run of consecutive tokens of one sequence x a group of
-// heads and streams every 32-key tile of the paged cache through shared memory ONCE for all of them (cp.async into a
+// heads and streams every 64-key tile of the paged cache through shared memory ONCE for all of them (cp.async into a
 // second buffer while the current one is used).  Per key tile, with 8 warps:
-//   1. scores:  the 32 x 32 block S = Q K^T is 2 x 4 blocks of 16 x 8, one per warp, over the full key width;
-//   2. softmax: each warp owns 4 rows (lane = key): mask, running maximum / sum, P = exp(S - m) as bf16, rescale factor;
+//   1. scores:  the 32 x 64 block S = Q K^T is 2 x 8 blocks of 16 x 8, two per warp (one A fragment feeds both; two
+//               accumulator sets alternate over the reduction so that consecutive MMAs do not wait on each other);
+//   2. softmax: each warp owns 4 rows, 8 lanes per row: mask, running maximum / sum, P = exp(S - m) as bf16, rescale factor;
 //   3. values:  O[32 x rank] += P V, warp = (16-row half, quarter of the value columns); V is the key tile itself.
-// A row's arithmetic depends only on its own position (32-aligned key tiles in ascending order): what else is in the
+// A row's arithmetic depends only on its own position (64-aligned key tiles in ascending order): what else is in the
 // CTA, the launch or the batch does not change its result.
 #include "blocks_common.cuh"
 
 namespace tlb {
 
 constexpr int kMRows = 32;   // query rows per CTA
-constexpr int kMKeys = 32;   // keys per tile
+constexpr int kMKeys = 64;   // keys per tile
+constexpr int kSS = kMKeys + 1;  // score row stride (floats)
+constexpr int kSP = kMKeys + 8;  // probability row stride (bf16): (stride / 8) odd
 constexpr int kMWarps = 8;
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3, const void *p) {
@@ -54,9 +57,9 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
     const int width = rank + rot;
     bf16 *sq = reinterpret_cast<bf16 *>(smem_raw);                  // [32][row_stride]
     bf16 *sk0 = sq + kMRows * row_stride;                           // 2 x [32][row_stride]
-    bf16 *sp = sk0 + 2 * kMKeys * row_stride;                       // [32][40]
-    float *ss = reinterpret_cast<float *>(sp + kMRows * 40);        // [32][33]
-    float *s_alpha = ss + kMRows * 33;                              // [32]
+    bf16 *sp = sk0 + 2 * kMKeys * row_stride;                       // [32][kSP]
+    float *ss = reinterpret_cast<float *>(sp + kMRows * kSP);       // [32][kSS]
+    float *s_alpha = ss + kMRows * kSS;                             // [32]
     float *s_l = s_alpha + kMRows;                                  // [32]
 
     const int first = tiles[blockIdx.x * 3 + 0], count = tiles[blockIdx.x * 3 + 1], seq = tiles[blockIdx.x * 3 + 2];
@@ -67,7 +70,7 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
     const int chunks = width / 8;  // 16-byte pieces of a cache row
 
     // zero everything once: padding columns of Q and K must read as zero in every product
-    for (int i = threadIdx.x; i < (3 * kMRows * row_stride) / 8; i += blockDim.x) reinterpret_cast<uint4 *>(sq)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < ((kMRows + 2 * kMKeys) * row_stride) / 8; i += blockDim.x) reinterpret_cast<uint4 *>(sq)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
     // queries: row = token-in-tile * head_group + head-in-group
     for (int r = warp; r < kMRows; r += kMWarps) {
@@ -99,16 +102,14 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
         cp_async_commit();
     };
 
-    // softmax state of the 4 rows this warp owns (uniform over the lanes)
-    float m_run[4], l_run[4];
-    int row_pos[4];
-    bool row_live[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        int r = warp * 4 + i, tq = r / head_group, hh = r % head_group;
-        m_run[i] = -INFINITY, l_run[i] = 0.f;
-        row_live[i] = tq < count && hh < nheads;
-        row_pos[i] = pos0 + tq;
+    // softmax state of the row this lane works on (a warp owns 4 rows, 8 lanes each; uniform over the 8 lanes)
+    float m_row = -INFINITY, l_row = 0.f;
+    int pos_row;
+    bool live_row;
+    {
+        int r = warp * 4 + (lane >> 3), tq = r / head_group, hh = r % head_group;
+        live_row = tq < count && hh < nheads;
+        pos_row = pos0 + tq;
     }
     const int mt = warp & 1, nt = warp >> 1;          // score block of this warp; nt is also its quarter of the value columns
     float acc[2 * PAIRS][4];
@@ -123,42 +124,70 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
         __syncthreads();  // this tile (and, first time, the queries) are in shared memory; every warp is done with the previous tile
         if (tile + 1 < n_tiles) stage(tile + 1, sk0 + ((tile + 1) & 1) * kMKeys * row_stride);  // lands while this tile is computed
 
-        // 1. scores
+        // 1. scores: this warp's row half x key blocks nt and nt + 4
         {
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            float ca0[4] = {}, ca1[4] = {}, cb0[4] = {}, cb1[4] = {};
             const bf16 *qa = sq + (mt * 16 + (lane & 15)) * row_stride + (lane >> 4) * 8;
-            const bf16 *kb = sk + (nt * 8 + (lane & 7)) * row_stride + ((lane >> 3) & 1) * 8;
-            for (int ks = 0; ks < ksteps; ++ks) {
-                uint32_t a0, a1, a2, a3, b0, b1;
+            const bf16 *kb = sk + ((nt + ((lane >> 4) & 1) * 4) * 8 + (lane & 7)) * row_stride + ((lane >> 3) & 1) * 8;
+            int ks = 0;
+            for (; ks + 1 < ksteps; ks += 2) {
+                uint32_t a0, a1, a2, a3, b0, b1, b2, b3, e0, e1, e2, e3, f0, f1, f2, f3;
                 ldmatrix_x4(a0, a1, a2, a3, qa + ks * 16);
-                ldmatrix_x2(b0, b1, kb + ks * 16);
-                mma_bf16(c, a0, a1, a2, a3, b0, b1);
+                ldmatrix_x4(b0, b1, b2, b3, kb + ks * 16);
+                ldmatrix_x4(e0, e1, e2, e3, qa + ks * 16 + 16);
+                ldmatrix_x4(f0, f1, f2, f3, kb + ks * 16 + 16);
+                mma_bf16(ca0, a0, a1, a2, a3, b0, b1);
+                mma_bf16(cb0, a0, a1, a2, a3, b2, b3);
+                mma_bf16(ca1, e0, e1, e2, e3, f0, f1);
+                mma_bf16(cb1, e0, e1, e2, e3, f2, f3);
+            }
+            if (ks < ksteps) {
+                uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                ldmatrix_x4(a0, a1, a2, a3, qa + ks * 16);
+                ldmatrix_x4(b0, b1, b2, b3, kb + ks * 16);
+                mma_bf16(ca0, a0, a1, a2, a3, b0, b1);
+                mma_bf16(cb0, a0, a1, a2, a3, b2, b3);
             }
             int g = lane >> 2, t = lane & 3;
-            float *o = ss + (mt * 16 + g) * 33 + nt * 8 + 2 * t;
-            o[0] = c[0] * scale, o[1] = c[1] * scale;
-            o[8 * 33] = c[2] * scale, o[8 * 33 + 1] = c[3] * scale;
+            float *o = ss + (mt * 16 + g) * kSS + nt * 8 + 2 * t;
+            o[0] = (ca0[0] + ca1[0]) * scale, o[1] = (ca0[1] + ca1[1]) * scale;
+            o[8 * kSS] = (ca0[2] + ca1[2]) * scale, o[8 * kSS + 1] = (ca0[3] + ca1[3]) * scale;
+            o[32] = (cb0[0] + cb1[0]) * scale, o[33] = (cb0[1] + cb1[1]) * scale;
+            o[8 * kSS + 32] = (cb0[2] + cb1[2]) * scale, o[8 * kSS + 33] = (cb0[3] + cb1[3]) * scale;
         }
         __syncthreads();
 
-        // 2. softmax over this tile's keys, 4 rows per warp
+        // 2. softmax over this tile's keys: a warp owns 4 rows, 8 lanes per row, 8 keys per lane (keys lq + 8 j)
         {
-            const int key = lo + tile * kMKeys + lane;
+            const int i = lane >> 3, lq = lane & 7, r = warp * 4 + i;
+            const int key0 = lo + tile * kMKeys + lq;
+            const int rp = pos_row;
+            const bool live = live_row;
+            float sv[8];
+            float mx = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                int r = warp * 4 + i;
-                bool vis = row_live[i] && key <= row_pos[i] && (window <= 0 || row_pos[i] - key < window);
-                float s = vis ? ss[r * 33 + lane] : -INFINITY;
-                float m_new = fmaxf(m_run[i], warp_max(s));
-                float alpha = m_new == -INFINITY ? 1.f : expf(m_run[i] - m_new);
-                float p = vis ? expf(s - m_new) : 0.f;
-                bf16 pb = __float2bfloat16_rn(p);
-                // the sum uses the rounded probability, so numerator and denominator see the same weights
-                l_run[i] = l_run[i] * alpha + warp_sum(__bfloat162float(pb));
-                m_run[i] = m_new;
-                sp[r * 40 + lane] = pb;
-                if (lane == 0) s_alpha[r] = alpha;
+            for (int j = 0; j < 8; ++j) {
+                int key = key0 + 8 * j;
+                bool vis = live && key <= rp && (window <= 0 || rp - key < window);
+                sv[j] = vis ? ss[r * kSS + lq + 8 * j] : -INFINITY;
+                mx = fmaxf(mx, sv[j]);
             }
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            float m_new = fmaxf(m_row, mx);
+            float alpha = m_new == -INFINITY ? 1.f : expf(m_row - m_new);
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                bf16 pb = __float2bfloat16_rn(sv[j] == -INFINITY ? 0.f : expf(sv[j] - m_new));
+                sum += __bfloat162float(pb);  // the rounded probability: numerator and denominator see the same weights
+                sp[r * kSP + lq + 8 * j] = pb;
+            }
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            l_row = l_row * alpha + sum;
+            m_row = m_new;
+            if (lq == 0) s_alpha[r] = alpha;
         }
         __syncthreads();
 
@@ -169,9 +198,9 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
 #pragma unroll
             for (int i = 0; i < 2 * PAIRS; ++i) acc[i][0] *= a_lo, acc[i][1] *= a_lo, acc[i][2] *= a_hi, acc[i][3] *= a_hi;
 #pragma unroll
-            for (int kk = 0; kk < 2; ++kk) {
+            for (int kk = 0; kk < kMKeys / 16; ++kk) {
                 uint32_t a0, a1, a2, a3;
-                ldmatrix_x4(a0, a1, a2, a3, sp + (mt * 16 + (lane & 15)) * 40 + kk * 16 + (lane >> 4) * 8);
+                ldmatrix_x4(a0, a1, a2, a3, sp + (mt * 16 + (lane & 15)) * kSP + kk * 16 + (lane >> 4) * 8);
                 const bf16 *vb = sk + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * row_stride + nt * (16 * PAIRS) + (lane >> 4) * 8;
 #pragma unroll
                 for (int pr = 0; pr < PAIRS; ++pr) {
@@ -184,9 +213,7 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
         }
     }
 
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-        if (lane == 0) s_l[warp * 4 + i] = l_run[i];
+    if ((lane & 7) == 0) s_l[warp * 4 + (lane >> 3)] = l_row;
     __syncthreads();
     {
         int g = lane >> 2, t = lane & 3;
@@ -225,14 +252,14 @@ extern "C" int tlb_latent_attention_mma(const void *q_lat, long long ql_token, l
     if (!q_lat || (!q_rot && rot > 0) || !slab || !block_table || !tiles || !tok_pos || !out || heads <= 0 || max_pages <= 0 || num_pages <= 0)
         return tl::fail(TL_EINVAL, "latent_attention_mma: bad argument");
     if (!tlb_latent_attention_mma_supported(rank, rot, page_size))
-        return tl::fail(TL_EINVAL, "latent_attention_mma: rank <= 512, (rank + rot) %% 8 == 0 and page_size %% 32 == 0 are required");
+        return tl::fail(TL_EINVAL, "latent_attention_mma: rank <= 512, (rank + rot) %% 8 == 0 and page_size %% 64 == 0 are required");
     if (!tl::aligned16(slab)) return tl::fail(TL_EINVAL, "latent_attention_mma: the cache must be 16-byte aligned");
     int width = rank + rot;
     int pairs = ceil_div(ceil_div(rank, 8), 8);            // value tiles (8 columns) -> pairs per quarter
     pairs = pairs <= 1 ? 1 : pairs <= 2 ? 2 : pairs <= 4 ? 4 : 8;
     int span = max(ceil_div(width, 16) * 16, 64 * pairs);  // columns a row must hold: the padded key width, the four value quarters
     int row_stride = span + 8;                              // (stride / 8) odd: conflict-free ldmatrix rows
-    size_t smem = (size_t)3 * kMRows * row_stride * 2 + kMRows * 40 * 2 + (size_t)kMRows * 33 * 4 + 2 * kMRows * 4;
+    size_t smem = (size_t)(kMRows + 2 * kMKeys) * row_stride * 2 + kMRows * kSP * 2 + (size_t)kMRows * kSS * 4 + 2 * kMRows * 4;
     int head_group = heads >= kMRows ? kMRows : heads;
     dim3 grid(num_tiles, ceil_div(heads, head_group));
     cudaStream_t st = as_stream(stream);

@@ -17,27 +17,30 @@ __device__ __forceinline__ float moe_act(float z, int act) {
     return 0.5f * z * (1.0f + tanhf(inner));
 }
 
-// One warp per token.  Logits live in shared memory [warps][experts].
+// One CTA per token: the row of h is staged in shared memory as fp32, the warps share the experts (each logit is one
+// warp's dot product in a fixed lane order, so it does not depend on the launch), then warp 0 picks the top-k.
 template <typename T>
-__global__ void moe_route_kernel(const T *__restrict__ h, const T *__restrict__ w, const T *__restrict__ b, int tokens, int dim, int experts,
-                                 int top, int32_t *__restrict__ idx, float *__restrict__ gate) {
-    extern __shared__ float logits[];
-    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int t = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (t >= tokens) return;
-    float *z = logits + warp * experts;
-    const T *x = h + (size_t)t * dim;
-    for (int e = 0; e < experts; ++e) {
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const T *__restrict__ h, const T *__restrict__ w, const T *__restrict__ b, int tokens, int dim, int experts, int top,
+                 int32_t *__restrict__ idx, float *__restrict__ gate) {
+    extern __shared__ float route_smem[];
+    float *x = route_smem;        // [dim]
+    float *z = route_smem + dim;  // [experts]
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) x[d] = to_f(h[(size_t)t * dim + d]);
+    __syncthreads();
+    for (int e = warp; e < experts; e += warps) {
         const T *row = w + (size_t)e * dim;
         float s = 0.f;
-        for (int d = lane; d < dim; d += 32) s = fmaf(to_f(x[d]), to_f(row[d]), s);
+        for (int d = lane; d < dim; d += 32) s = fmaf(x[d], to_f(row[d]), s);
         s = warp_sum(s);
         if (lane == 0) z[e] = s + (b ? to_f(b[e]) : 0.f);
     }
-    __syncwarp();
-    // top-k by repeated arg-max over the warp (lower index wins a tie)
-    float chosen_v = 0.f, first_v = 0.f, denom = 0.f;
-    int chosen_i = 0;
+    __syncthreads();
+    if (warp != 0) return;
+    // top-k by repeated arg-max over the warp (lower index wins a tie); weights = softmax over the chosen logits
+    float first_v = 0.f, denom = 0.f;
     for (int k = 0; k < top; ++k) {
         float bv = -INFINITY;
         int bi = 0x7fffffff;
@@ -53,21 +56,14 @@ __global__ void moe_route_kernel(const T *__restrict__ h, const T *__restrict__ 
         if (k == 0) first_v = bv;
         float p = expf(bv - first_v);  // the first choice is the largest logit
         denom += p;
-        if (lane == k % 32 && k < 32) chosen_v = p, chosen_i = bi;
-        if (k >= 32 && lane == 0) {  // more than 32 choices: write straight through, normalised below
+        if (lane == 0) {
             idx[(size_t)t * top + k] = bi;
             gate[(size_t)t * top + k] = p;
+            if (bi != 0x7fffffff) z[bi] = -INFINITY;
         }
         __syncwarp();
-        if (lane == 0 && bi != 0x7fffffff) z[bi] = -INFINITY;
-        __syncwarp();
     }
-    if (lane < top && lane < 32) {
-        idx[(size_t)t * top + lane] = chosen_i;
-        gate[(size_t)t * top + lane] = chosen_v / denom;
-    }
-    if (top > 32 && lane == 0)
-        for (int k = 32; k < top; ++k) gate[(size_t)t * top + k] /= denom;
+    for (int k = lane; k < top; k += 32) gate[(size_t)t * top + k] /= denom;
 }
 
 // Single CTA: histogram, padded exclusive scan, scatter.
@@ -305,12 +301,11 @@ int tlb_moe_route(const void *h, const void *w, const void *b, int tokens, int d
                   void *stream) {
     if (tokens <= 0) return TL_OK;
     if (!h || !w || !idx || !gate || dim <= 0 || experts <= 0 || top <= 0 || top > experts) return tl::fail(TL_EINVAL, "moe_route: bad argument");
-    const int warps = 4;
-    size_t smem = (size_t)warps * experts * sizeof(float);
-    if (smem > 48 * 1024) return tl::fail(TL_EINVAL, "moe_route: %d experts do not fit", experts);
+    size_t smem = ((size_t)dim + experts) * sizeof(float);
+    if (smem > 48 * 1024) return tl::fail(TL_EINVAL, "moe_route: width %d + %d experts do not fit", dim, experts);
     TLB_DISPATCH(dtype, "moe_route",
-                 moe_route_kernel<T><<<ceil_div(tokens, warps), warps * 32, smem, as_stream(stream)>>>((const T *)h, (const T *)w, (const T *)b, tokens,
-                                                                                                      dim, experts, top, idx, gate));
+                 moe_route_kernel<T><<<tokens, 256, smem, as_stream(stream)>>>((const T *)h, (const T *)w, (const T *)b, tokens, dim, experts, top, idx,
+                                                                             gate));
     TL_LAUNCH_CHECK("moe_route");
     return TL_OK;
 }

@@ -30,7 +30,9 @@ class RaggedEntry:
 
 
 class RaggedPlan:
-    def __init__(self, entries: Sequence[RaggedEntry], device, tile):
+    def __init__(self, entries: Sequence[RaggedEntry], device, tile, max_pages: int | None = None, into: torch.Tensor | None = None):
+        """``max_pages`` fixes the block table's width (at least what the longest request needs) and ``into`` names a
+        preallocated int32 device block to upload into: a captured graph reads the same addresses every step."""
         sizes = sorted({int(tile)} if isinstance(tile, int) else {int(t) for t in tile})
         owners = []
         for e in entries:
@@ -52,7 +54,12 @@ class RaggedPlan:
             raise
         T = sum(len(e.tokens) for e in entries)
         S = len(entries)
-        max_pages = max(o.num_pages for o in owners)
+        needed = max(o.num_pages for o in owners)
+        if max_pages is not None and max_pages < needed:
+            for o, n in done:
+                o.rewind(n)
+            raise ValueError(f"block table of {max_pages} pages, {needed} needed")
+        max_pages = needed if max_pages is None else max_pages
         wants = [list(e.want) if e.want is not None else [len(e.tokens) - 1] for e in entries]
         W = sum(len(w) for w in wants)
         n_tiles = {size: sum(-(-len(e.tokens) // size) for e in entries) for size in sizes}
@@ -88,7 +95,14 @@ class RaggedPlan:
             buf[start : start + 3 * n] = np.asarray(tile_rows[size], dtype=np.int32).reshape(-1)
         self.num_tokens, self.num_seqs, self.num_want, self.max_pages = T, S, W, max_pages
         self.h2d_bytes = total * 4
-        dev = host.to(device, non_blocking=True)
+        if into is None:
+            dev = host.to(device, non_blocking=True)
+        else:
+            if into.numel() != total or into.dtype != torch.int32:
+                raise ValueError("the device block does not fit this plan")
+            dev = into
+            dev.copy_(host[:total], non_blocking=True)
+        self.total_ints = total
         self._host = host  # keep the pinned block alive until the copy has run
         self.ids, self.tok_pos, self.tok_seq = dev[0:T], dev[T : 2 * T], dev[2 * T : 3 * T]
         self.want_rows = dev[3 * T : 3 * T + W]

@@ -19,6 +19,8 @@ bf16 (serving) or fp32 (every product in true fp32); norms, softmax, router, res
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from extensions_b200.tiny_llm_ext_b200 import blocks
@@ -55,6 +57,11 @@ class VoluzenModel:
         self.num_hidden_layers = len(config["layers"])
         self.page_size = page_size
         self.h2d_bytes = 0
+        # Decode-only steps (every entry brings one token) replay a captured CUDA graph, one per (number of entries, block
+        # table width); the step's integers are data in one device block.  None = on for CUDA, False = always eager.
+        self.use_decode_graph: bool | None = None if os.environ.get("TL_VOLUZEN_GRAPH", "1") != "0" else False
+        self._graphs: dict = {}
+        self.graph_replays = self.graph_captures = 0
 
         def take(name: str) -> torch.Tensor:
             if name not in tensors:
@@ -130,9 +137,52 @@ class VoluzenModel:
     def forward_ragged(self, entries: list[RaggedEntry]) -> torch.Tensor:
         """One step over ``entries`` -> fp32 logits ``[sum of wanted places, vocab]`` in entry order.  Appends the
         entries' tokens to their caches."""
+        if self.use_decode_graph is not False and self.device.type == "cuda" and all(len(e.tokens) == 1 and (e.want is None or list(e.want) == [0]) for e in entries):
+            return self._decode_step(entries)
         plan = RaggedPlan(entries, self.device, self.tile_sizes)
         self.h2d_bytes += plan.h2d_bytes
         return self._forward_plan(plan)
+
+    def _decode_step(self, entries: list[RaggedEntry]) -> torch.Tensor:
+        """A step of one token per entry.  The first step of a shape runs eagerly (it warms every library up), the second
+        is captured - its integers uploaded into the graph's own device block - and from then on a step is one
+        host-to-device copy and one replay.  Shapes: the number of entries and the block table's width (a power of two,
+        at least 4 pages), so a request growing by a page does not change the graph; slabs that moved do."""
+        S = len(entries)
+        pages = max(-(-(getattr(e.cache[0], "owner", e.cache[0]).offset + 1) // self.page_size) for e in entries)
+        width = 4
+        while width < pages:
+            width *= 2
+        key = (S, width)
+        state = self._graphs.get(key)
+        if state is not None and state.get("slabs") not in (None, self.page_pool.slab_version):
+            state = None  # captured against slabs that have been reallocated since
+        if state is None:
+            self._graphs[key] = {"slabs": None}
+            plan = RaggedPlan(entries, self.device, self.tile_sizes)
+            self.h2d_bytes += plan.h2d_bytes
+            return self._forward_plan(plan)
+        if state["slabs"] is None:
+            total = 3 * S + S + S * width + 3 * S * len(self.tile_sizes)
+            state["block"] = torch.zeros(total, dtype=torch.int32, device=self.device)
+            plan = RaggedPlan(entries, self.device, self.tile_sizes, max_pages=width, into=state["block"])
+            state["slabs"] = self.page_pool.slab_version  # the append may have grown the pool: read it after the plan
+            torch.cuda.current_stream(self.device).synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                state["logits"] = self._forward_plan(plan)
+            state["graph"], state["plan"] = graph, plan
+            self.graph_captures += 1
+        else:
+            plan = RaggedPlan(entries, self.device, self.tile_sizes, max_pages=width, into=state["block"])
+            if self.page_pool.slab_version != state["slabs"]:  # this very append moved the slabs: run it eagerly, re-capture next time
+                self._graphs.pop(key)
+                return self._forward_plan(plan)
+            state["host"] = plan._host
+        self.h2d_bytes += plan.h2d_bytes
+        state["graph"].replay()
+        self.graph_replays += 1
+        return state["logits"].clone()
 
     def _forward_plan(self, plan: RaggedPlan) -> torch.Tensor:
         exact = self.precision == torch.float32
