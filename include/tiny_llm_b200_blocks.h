@@ -73,7 +73,11 @@ int tlb_latent_attention_mma_supported(int rank, int rot, int page_size);
 int tlb_latent_attention_mma(const void *q_lat, long long ql_token, long long ql_head, const void *q_rot, long long qr_token,
                              long long qr_head, const void *slab, int num_pages, int page_size, int rank, int rot,
                              const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles, const int32_t *tok_pos,
-                             int heads, int window, float scale, void *out, long long o_token, long long o_head, void *stream);
+                             int heads, int window, float scale, void *out, long long o_token, long long o_head, int splits,
+                             void *workspace, size_t workspace_bytes, void *stream);
+/* splits > 1 cuts every tile's key range over that many CTAs (flash decoding: few query rows, long contexts) and a second
+ * launch merges the partial sums; workspace: tlb_latent_attention_mma_workspace(...) bytes, no initialisation needed. */
+size_t tlb_latent_attention_mma_workspace(int num_tiles, int heads, int rank, int splits);
 
 /* out[t, j] = act(gu[t, j]) * gu[t, width + j]; act 0 = silu, 1 = gelu (tanh form). */
 int tlb_gated_act(const void *gu, void *out, int rows, int width, int act, int dtype, void *stream);

@@ -149,7 +149,8 @@ def run_attention(dev, dtype, q_full, rows, positions, rank, window, scale, page
         tiles.append((first, n, 0))
         first += n
     blocks.latent_attention(q[:, :, :rank], q[:, :, rank:], slab, table, torch.tensor(tiles, dtype=torch.int32, device=dev),
-                            positions.to(torch.int32).to(dev), window=window, scale=scale, out=out.transpose(0, 1), kernel=chosen)
+                            positions.to(torch.int32).to(dev), window=window, scale=scale, out=out.transpose(0, 1), kernel=chosen,
+                            max_context=S)  # few query rows over a long cache: the key range is split over CTAs and merged
     return out.transpose(0, 1)
 
 
@@ -170,9 +171,9 @@ def test_latent_attention_against_plain_attention(dev, dtype, rank, rot, heads):
 @pytest.mark.parametrize("rank,rot,heads", [(32, 8, 1), (96, 16, 4), (130, 6, 5), (64, 32, 16), (256, 64, 40), (512, 64, 3)])
 def test_tensor_core_attention_against_plain_attention_and_the_general_kernel(dev, rank, rot, heads):
     g = torch.Generator().manual_seed(rank + heads)
-    S = 200
+    S = 520
     rows = torch.randn(S, rank + rot, generator=g).to(torch.bfloat16)
-    positions = torch.tensor(list(range(0, 9)) + [30, 31, 32, 33, 34, 63, 64, 65] + list(range(120, 150)) + [199])
+    positions = torch.tensor(list(range(0, 9)) + [30, 31, 32, 33, 34, 63, 64, 65] + list(range(120, 150)) + [199, 383, 384, 519])
     q = torch.randn(len(positions), heads, rank + rot, generator=g).to(torch.bfloat16)
     for window in (0, 1, 33, 64):
         want = O.cache_attention(q.double(), rows.double(), positions, rank, window, 0.09)
@@ -345,7 +346,8 @@ def test_prefill_then_token_by_token_decoding_across_windows_and_pages(dev, name
         eager = run_schedule(model, {"a": prompt}, [[("a", 190)]] + [[("a", 1)]] * 120)["a"]
     finally:
         model.use_decode_graph = None
-    assert row_error(eager, got.double()) < (1e-6 if dtype == torch.float32 else 1e-2)
+    # (bfloat16: the captured step may cut the key range over another number of CTAs than the eager one: rounding)
+    assert row_error(eager, got.double()) < (1e-6 if dtype == torch.float32 else 5e-2)
     alone = run_schedule(model, {"a": prompt[:30]}, [[("a", 1)]] * 30)["a"]  # the first tokens, one by one from nothing
     assert rows_match(alone, want[:30], dtype)
 

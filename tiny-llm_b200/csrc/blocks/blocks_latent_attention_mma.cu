@@ -52,7 +52,8 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
                             long long qr_head, const bf16 *__restrict__ slab, int num_pages, int page_size, int rank, int rot,
                             const int32_t *__restrict__ block_table, int max_pages, const int32_t *__restrict__ tiles,
                             const int32_t *__restrict__ tok_pos, int heads, int head_group, int window, float scale, bf16 *__restrict__ out,
-                            long long o_token, long long o_head, int row_stride /* shared-memory row stride in elements */) {
+                            long long o_token, long long o_head, int row_stride /* shared-memory row stride in elements */,
+                            float *__restrict__ part /* split results, or NULL */) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int width = rank + rot;
     bf16 *sq = reinterpret_cast<bf16 *>(smem_raw);                  // [32][row_stride]
@@ -93,11 +94,14 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
         bool ok = page >= 0 && page < num_pages;
         int valid = ok ? min(kMKeys, hi - k0 + 1) : 0;
         const bf16 *src = slab + ((size_t)(ok ? page : 0) * page_size + (k0 % page_size)) * width;
-        for (int c = threadIdx.x; c < kMKeys * chunks; c += blockDim.x) {
-            int j = c / chunks, piece = c - j * chunks;
-            bf16 *d = dst + j * row_stride + piece * 8;
-            if (j < valid) cp_async16(d, src + (size_t)j * width + piece * 8);
-            else *reinterpret_cast<uint4 *>(d) = make_uint4(0, 0, 0, 0);
+        for (int j = warp; j < kMKeys; j += kMWarps) {  // a warp copies whole rows: no index arithmetic beyond an add
+            bf16 *d = dst + j * row_stride;
+            const bf16 *g = src + (size_t)j * width;
+            if (j < valid) {
+                for (int piece = lane; piece < chunks; piece += 32) cp_async16(d + piece * 8, g + piece * 8);
+            } else {
+                for (int piece = lane; piece < chunks; piece += 32) *reinterpret_cast<uint4 *>(d + piece * 8) = make_uint4(0, 0, 0, 0);
+            }
         }
         cp_async_commit();
     };
@@ -116,13 +120,17 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
 #pragma unroll
     for (int i = 0; i < 2 * PAIRS; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
-    stage(0, sk0);
+    // with the key range split over gridDim.z CTAs, this one takes a contiguous run of key tiles
+    const int per_split = (n_tiles + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int tile_begin = (int)blockIdx.z * per_split, tile_end = min(n_tiles, tile_begin + per_split);
+    if (tile_begin < tile_end) stage(tile_begin, sk0 + (tile_begin & 1) * kMKeys * row_stride);
     const int ksteps = (width + 15) / 16;
-    for (int tile = 0; tile < n_tiles; ++tile) {
+    __syncthreads();  // the queries are staged (also when this split has no tile)
+    for (int tile = tile_begin; tile < tile_end; ++tile) {
         bf16 *sk = sk0 + (tile & 1) * kMKeys * row_stride;
         cp_async_wait<0>();
-        __syncthreads();  // this tile (and, first time, the queries) are in shared memory; every warp is done with the previous tile
-        if (tile + 1 < n_tiles) stage(tile + 1, sk0 + ((tile + 1) & 1) * kMKeys * row_stride);  // lands while this tile is computed
+        __syncthreads();  // this tile is in shared memory; every warp is done with the previous tile
+        if (tile + 1 < tile_end) stage(tile + 1, sk0 + ((tile + 1) & 1) * kMKeys * row_stride);  // lands while this tile is computed
 
         // 1. scores: this warp's row half x key blocks nt and nt + 4
         {
@@ -213,8 +221,26 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
         }
     }
 
-    if ((lane & 7) == 0) s_l[warp * 4 + (lane >> 3)] = l_row;
+    __syncthreads();  // the last tile's rescale factors have been read
+    if ((lane & 7) == 0) s_l[warp * 4 + (lane >> 3)] = l_row, s_alpha[warp * 4 + (lane >> 3)] = m_row;
     __syncthreads();
+    if (part != nullptr) {
+        // split results: [cta (x, y)][split][32 rows][value columns + 2] fp32: un-normalised sums, then the maximum and the sum
+        const int cols = 64 * PAIRS + 2;
+        float *dst = part + (((size_t)blockIdx.y * gridDim.x + blockIdx.x) * gridDim.z + blockIdx.z) * kMRows * cols;
+        int g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            int r = mt * 16 + g + half * 8;
+#pragma unroll
+            for (int i = 0; i < 2 * PAIRS; ++i) {
+                int col = nt * (16 * PAIRS) + i * 8 + 2 * t;
+                dst[r * cols + col] = acc[i][half * 2], dst[r * cols + col + 1] = acc[i][half * 2 + 1];
+            }
+        }
+        if (threadIdx.x < kMRows) dst[threadIdx.x * cols + 64 * PAIRS] = s_alpha[threadIdx.x], dst[threadIdx.x * cols + 64 * PAIRS + 1] = s_l[threadIdx.x];
+        return;
+    }
     {
         int g = lane >> 2, t = lane & 3;
 #pragma unroll
@@ -233,9 +259,56 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
     }
 }
 
+// Combine the split results of one query row per CTA: weights exp(m_z - max m), added in split order.
+__global__ void __launch_bounds__(128)
+latent_attention_merge_kernel(const float *__restrict__ part, int splits, int cols, const int32_t *__restrict__ tiles, int heads, int head_group,
+                              int rank, bf16 *__restrict__ out, long long o_token, long long o_head) {
+    __shared__ float weight[64];
+    __shared__ float inv_l;
+    const int first = tiles[blockIdx.x * 3 + 0], count = tiles[blockIdx.x * 3 + 1];
+    const int head0 = blockIdx.y * head_group, nheads = min(head_group, heads - head0);
+    const int r = blockIdx.z, tq = r / head_group, hh = r % head_group;
+    if (tq >= count || hh >= nheads) return;
+    const float *base = part + (((size_t)blockIdx.y * gridDim.x + blockIdx.x) * splits * kMRows + r) * cols;
+    const size_t step = (size_t)kMRows * cols;  // from one split's row to the next split's
+    if (threadIdx.x < 32) {
+        float m = -INFINITY;
+        for (int z = threadIdx.x; z < splits; z += 32) m = fmaxf(m, base[z * step + cols - 2]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int z = threadIdx.x; z < splits; z += 32) {
+            float mz = base[z * step + cols - 2];
+            float w = mz == -INFINITY ? 0.f : expf(mz - m);
+            weight[z] = w;
+            l += base[z * step + cols - 1] * w;
+        }
+        l = warp_sum(l);
+        if (threadIdx.x == 0) inv_l = 1.0f / l;
+    }
+    __syncthreads();
+    bf16 *o = out + (size_t)(first + tq) * o_token + (size_t)(head0 + hh) * o_head;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        float v = 0.f;
+        for (int z = 0; z < splits; ++z) v = fmaf(base[z * step + c], weight[z], v);
+        o[c] = __float2bfloat16_rn(v * inv_l);
+    }
+}
+
 }  // namespace tlb
 
 using namespace tlb;
+
+static int mma_pairs(int rank) {
+    int pairs = ceil_div(ceil_div(rank, 8), 8);  // value tiles (8 columns) -> pairs per quarter
+    return pairs <= 1 ? 1 : pairs <= 2 ? 2 : pairs <= 4 ? 4 : 8;
+}
+
+// Bytes of workspace for `splits` > 1 (0 for one split).
+extern "C" size_t tlb_latent_attention_mma_workspace(int num_tiles, int heads, int rank, int splits) {
+    if (splits <= 1) return 0;
+    int head_group = heads >= kMRows ? kMRows : heads;
+    return (size_t)num_tiles * ceil_div(heads, head_group) * splits * kMRows * (64 * mma_pairs(rank) + 2) * sizeof(float);
+}
 
 // Rows of a CTA: `tile_tokens` consecutive tokens x `head_group` heads, head_group = min(heads, 32), tile_tokens = 32 / head_group.
 extern "C" int tlb_latent_attention_mma_tile_tokens(int heads) { return heads >= kMRows ? 1 : kMRows / heads; }
@@ -247,7 +320,8 @@ extern "C" int tlb_latent_attention_mma_supported(int rank, int rot, int page_si
 extern "C" int tlb_latent_attention_mma(const void *q_lat, long long ql_token, long long ql_head, const void *q_rot, long long qr_token,
                                         long long qr_head, const void *slab, int num_pages, int page_size, int rank, int rot,
                                         const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles, const int32_t *tok_pos,
-                                        int heads, int window, float scale, void *out, long long o_token, long long o_head, void *stream) {
+                                        int heads, int window, float scale, void *out, long long o_token, long long o_head, int splits,
+                                        void *workspace, size_t workspace_bytes, void *stream) {
     if (num_tiles <= 0) return TL_OK;
     if (!q_lat || (!q_rot && rot > 0) || !slab || !block_table || !tiles || !tok_pos || !out || heads <= 0 || max_pages <= 0 || num_pages <= 0)
         return tl::fail(TL_EINVAL, "latent_attention_mma: bad argument");
@@ -255,13 +329,17 @@ extern "C" int tlb_latent_attention_mma(const void *q_lat, long long ql_token, l
         return tl::fail(TL_EINVAL, "latent_attention_mma: rank <= 512, (rank + rot) %% 8 == 0 and page_size %% 64 == 0 are required");
     if (!tl::aligned16(slab)) return tl::fail(TL_EINVAL, "latent_attention_mma: the cache must be 16-byte aligned");
     int width = rank + rot;
-    int pairs = ceil_div(ceil_div(rank, 8), 8);            // value tiles (8 columns) -> pairs per quarter
-    pairs = pairs <= 1 ? 1 : pairs <= 2 ? 2 : pairs <= 4 ? 4 : 8;
+    int pairs = mma_pairs(rank);
+    if (splits < 1) splits = 1;
+    if (splits > 64) splits = 64;
+    if (splits > 1 && (!workspace || workspace_bytes < tlb_latent_attention_mma_workspace(num_tiles, heads, rank, splits)))
+        return tl::fail(TL_EWORKSPACE, "latent_attention_mma: workspace missing or too small for %d splits", splits);
+    float *part = splits > 1 ? (float *)workspace : nullptr;
     int span = max(ceil_div(width, 16) * 16, 64 * pairs);  // columns a row must hold: the padded key width, the four value quarters
     int row_stride = span + 8;                              // (stride / 8) odd: conflict-free ldmatrix rows
     size_t smem = (size_t)(kMRows + 2 * kMKeys) * row_stride * 2 + kMRows * kSP * 2 + (size_t)kMRows * kSS * 4 + 2 * kMRows * 4;
     int head_group = heads >= kMRows ? kMRows : heads;
-    dim3 grid(num_tiles, ceil_div(heads, head_group));
+    dim3 grid(num_tiles, ceil_div(heads, head_group), splits);
     cudaStream_t st = as_stream(stream);
 #define TLB_LAM(P)                                                                                                                          \
     do {                                                                                                                                    \
@@ -272,7 +350,7 @@ extern "C" int tlb_latent_attention_mma(const void *q_lat, long long ql_token, l
         }                                                                                                                                   \
         kernel<<<grid, kMWarps * 32, smem, st>>>((const bf16 *)q_lat, ql_token, ql_head, (const bf16 *)(q_rot ? q_rot : q_lat), qr_token,   \
                                                  qr_head, (const bf16 *)slab, num_pages, page_size, rank, rot, block_table, max_pages, tiles, \
-                                                 tok_pos, heads, head_group, window, scale, (bf16 *)out, o_token, o_head, row_stride);      \
+                                                 tok_pos, heads, head_group, window, scale, (bf16 *)out, o_token, o_head, row_stride, part); \
     } while (0)
     if (pairs == 1) TLB_LAM(1);
     else if (pairs == 2) TLB_LAM(2);
@@ -280,5 +358,10 @@ extern "C" int tlb_latent_attention_mma(const void *q_lat, long long ql_token, l
     else TLB_LAM(8);
 #undef TLB_LAM
     TL_LAUNCH_CHECK("latent_attention_mma");
+    if (splits > 1) {
+        latent_attention_merge_kernel<<<dim3(num_tiles, ceil_div(heads, head_group), kMRows), 128, 0, st>>>(part, splits, 64 * pairs + 2, tiles, heads, head_group,
+                                                                                                   rank, (bf16 *)out, o_token, o_head);
+        TL_LAUNCH_CHECK("latent_attention_merge");
+    }
     return TL_OK;
 }

@@ -31,7 +31,9 @@ _SIGNATURES = {
     "tlb_latent_attention": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _VP, _LL, _LL, _I, _VP]),
     "tlb_latent_attention_mma_tile_tokens": (_I, [_I]),
     "tlb_latent_attention_mma_supported": (_I, [_I, _I, _I]),
-    "tlb_latent_attention_mma": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _VP, _LL, _LL, _VP]),
+    "tlb_latent_attention_mma": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _VP, _LL, _LL, _I, _VP,
+                                      ctypes.c_size_t, _VP]),
+    "tlb_latent_attention_mma_workspace": (ctypes.c_size_t, [_I, _I, _I, _I]),
     "tlb_gated_act": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
     "tlb_moe_route": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _VP, _VP, _I, _VP]),
     "tlb_moe_max_rows": (_LL, [_I, _I, _I]),
@@ -187,10 +189,26 @@ def attention_kernel(dtype, heads: int, rank: int, rot: int, page_size: int) -> 
     return "general", ATTENTION_TILE_TOKENS
 
 
-def latent_attention(q_lat, q_rot, slab, block_table, tiles, tok_pos, *, window: int, scale: float, out, kernel: str = "general"):
+_SM_COUNT: dict = {}
+
+
+def attention_splits(num_ctas: int, max_context: int, device) -> int:
+    """Into how many CTAs to cut every tile's key range: 1 while the launch fills the GPU by itself, else enough to give
+    every SM a CTA, each with at least two 64-key tiles."""
+    key = torch.device(device)
+    if key not in _SM_COUNT:
+        _SM_COUNT[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    sms = _SM_COUNT[key]
+    if num_ctas * 2 > sms:
+        return 1
+    return max(1, min(sms // num_ctas, max_context // 128, 32))
+
+
+def latent_attention(q_lat, q_rot, slab, block_table, tiles, tok_pos, *, window: int, scale: float, out, kernel: str = "general", max_context: int = 0):
     """``q_lat [T, H, rank]``, ``q_rot [T, H, rot]`` and ``out [T, H, rank]`` are views with arbitrary token / head strides
     and unit inner stride; ``tiles [n, 3]`` int32 (first token, count, block-table row) cut for the tile size that
-    ``attention_kernel`` gives beside the kernel's name."""
+    ``attention_kernel`` gives beside the kernel's name.  ``max_context`` (the longest sequence of the step, 0 = unknown)
+    lets the tensor-core kernel split the key range over several CTAs when the launch alone would leave SMs idle."""
     _gpu("latent_attention", q_lat, q_rot, slab, block_table, tiles, tok_pos, out)
     _contig("latent_attention", slab, block_table, tiles, tok_pos)
     T, H, rank = q_lat.shape
@@ -204,9 +222,14 @@ def latent_attention(q_lat, q_rot, slab, block_table, tiles, tok_pos, *, window:
     if kernel == "mma":
         if slab.dtype != torch.bfloat16:
             raise RuntimeError("latent_attention: the tensor-core kernel takes a bfloat16 cache")
+        reach = min(max_context, int(window)) if window else max_context  # keys a query can see at most
+        splits = attention_splits(tiles.shape[0] * -(-H // 32), reach, slab.device) if reach else 1
+        nbytes = int(lib.tlb_latent_attention_mma_workspace(tiles.shape[0], H, rank, splits))
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=slab.device) if nbytes else None
         _check(lib.tlb_latent_attention_mma(_ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(slab), P,
                                             page_size, rank, rot, _ptr(block_table), block_table.shape[1], _ptr(tiles), tiles.shape[0], _ptr(tok_pos),
-                                            H, int(window or 0), float(scale), _ptr(out), out.stride(0), out.stride(1), _stream(slab)))
+                                            H, int(window or 0), float(scale), _ptr(out), out.stride(0), out.stride(1), splits, _ptr(ws), nbytes,
+                                            _stream(slab)))
         return out
     if kernel != "general":
         raise RuntimeError(f"latent_attention: unknown kernel {kernel!r}")

@@ -65,6 +65,7 @@ class LatentAttention:
         q_lat = torch.bmm(q3[:, :, :dn].transpose(0, 1), self.w_uk)          # [H, T, rank]
         o_lat = torch.empty_like(q_lat)
         blocks.latent_attention(q_lat.transpose(0, 1), q3[:, :, dn:], slab, plan.block_table, plan.tiles_for(tile_tokens), plan.tok_pos,
-                                window=self.window, scale=self.scale, out=o_lat.transpose(0, 1), kernel=kernel)
+                                window=self.window, scale=self.scale, out=o_lat.transpose(0, 1), kernel=kernel,
+                                max_context=getattr(plan, "max_context", 0))
         o = torch.bmm(o_lat, self.w_uv_t)                                     # [H, T, vdim]
         return linear(o.transpose(0, 1).reshape(T, H * self.vdim), self.w_o)

@@ -109,6 +109,7 @@ class RaggedPlan:
         self.block_table = dev[3 * T + W : 3 * T + W + S * max_pages].view(S, max_pages)
         self._tiles = {size: dev[start : start + 3 * n].view(n, 3) for size, (start, n) in tile_at.items()}
         self.tiles = self._tiles[sizes[0]]
+        self.max_context = max(o.offset for o in owners)  # the longest sequence after this step's append
         self.want_counts = [len(x) for x in wants]
         self.starts = starts
 
