@@ -53,6 +53,14 @@ int tlb_latent_append(const void *down, const void *norm_w, float eps, int rank,
                       const int32_t *tok_pos, const int32_t *tok_seq, const int32_t *block_table, int max_pages, int num_pages,
                       int page_size, void *slab, int tokens, int dtype, void *stream);
 
+/* The append with two more things for a fused q|dkv projection: the token's row of `down` is down_stride elements apart
+ * (it may be a slice of a wider row), and, when q != NULL, the same launch rotates `rot_dims` entries from q_first in each
+ * of q_heads query heads of q[t,:] (q_stride / q_head_stride in elements) in place, with the angles of the shared key part. */
+int tlb_latent_prepare(const void *down, long long down_stride, const void *norm_w, float eps, int rank, int rot, int rot_dims, int interleaved,
+                       double base, const int32_t *tok_pos, const int32_t *tok_seq, const int32_t *block_table, int max_pages, int num_pages,
+                       int page_size, void *slab, void *q, long long q_stride, int q_heads, int q_head_stride, int q_first, int tokens, int dtype,
+                       void *stream);
+
 /* Latent (absorbed multi-query) attention over the paged latent cache.  Query row (t, h) is the concatenation of
  * q_lat[t,h,0:rank] and q_rot[t,h,0:rot] (two pointers with token / head strides in elements); key j of the token's
  * sequence is slab row j (rank + rot entries), value j its first `rank` entries.  Token t sees keys j <= tok_pos[t] and,

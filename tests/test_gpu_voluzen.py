@@ -233,6 +233,32 @@ def test_latent_append_norms_rotates_and_lands_on_the_right_slot(dev, dtype, int
     assert int((slab.float().abs().sum(-1) > 0).sum()) == written  # nothing else was touched
 
 
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_fused_prepare_rotates_the_queries_and_fills_the_cache_in_one_launch(dev, interleaved):
+    heads, dn, dr, rank, page = 3, 10, 8, 24, 32
+    g = torch.Generator().manual_seed(13)
+    qd = torch.randn(5, heads * (dn + dr) + rank + dr, generator=g)
+    w = 1 + 0.1 * torch.randn(rank, generator=g)
+    pos = torch.tensor([31, 32, 33, 7, 8], dtype=torch.int32)
+    seq = torch.tensor([0, 0, 0, 1, 1], dtype=torch.int32)
+    table = torch.tensor([[2, 0], [1, -1]], dtype=torch.int32)
+    slab = torch.zeros((3, page, rank + dr), device=dev)
+    got = qd.to(dev).clone()
+    blocks.latent_prepare(got, w.to(dev), 1e-5, heads=heads, dim=dn, rot_dim=dr, rank=rank, rot_dims=dr, interleaved=interleaved, base=3000.0,
+                          tok_pos=pos.to(dev), tok_seq=seq.to(dev), block_table=table.to(dev), slab=slab)
+    q_width = heads * (dn + dr)
+    want_q = qd[:, :q_width].double().reshape(5, heads, dn + dr).clone()
+    want_q[..., dn:] = O.rotate(want_q[..., dn:], pos, dr, 3000.0, interleaved)
+    close(got[:, :q_width].reshape(5, heads, dn + dr), want_q, 2e-6)
+    assert torch.equal(got[:, q_width:].cpu(), qd[:, q_width:])  # the latent's columns are read, not written
+    c = O.norm_plain(qd[:, q_width : q_width + rank].double(), w.double(), 1e-5)
+    kr = O.rotate(qd[:, q_width + rank :].double(), pos, dr, 3000.0, interleaved)
+    for t in range(5):
+        row = slab[int(table[seq[t], pos[t] // page]), pos[t] % page].cpu()
+        close(row[:rank], c[t], 2e-6)
+        close(row[rank:], kr[t], 2e-6)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("experts,top,shared", [(6, 2, True), (5, 1, False), (4, 4, True), (40, 3, False)])
 def test_router_and_experts_against_the_loop_over_tokens(dev, dtype, experts, top, shared):

@@ -89,12 +89,26 @@ __global__ void rope_rows_kernel(T *x, long long row_stride, long long head_stri
 template <typename T>
 __global__ void latent_append_kernel(const T *__restrict__ down, const T *__restrict__ norm_w, float eps, int rank, int rot, int rot_dims,
                                      int interleaved, double log2_base, const int32_t *__restrict__ tok_pos, const int32_t *__restrict__ tok_seq,
-                                     const int32_t *__restrict__ block_table, int max_pages, int num_pages, int page_size, T *__restrict__ slab) {
+                                     const int32_t *__restrict__ block_table, int max_pages, int num_pages, int page_size, T *__restrict__ slab,
+                                     long long down_stride, T *q, long long q_stride, int q_heads, int q_head_stride, int q_first) {
     __shared__ float scratch[33];
     int t = blockIdx.x;
     int pos = tok_pos[t];
     int width = rank + rot;
-    const T *src = down + (size_t)t * width;
+    const T *src = down + (size_t)t * down_stride;
+    if (q != nullptr) {  // the same launch rotates the token's query heads in place (same angles as the shared key part)
+        int half = rot_dims / 2;
+        for (int i = threadIdx.x; i < half * q_heads; i += blockDim.x) {
+            int hd = i / half, k = i - hd * half;
+            float c, s;
+            rope_angle(pos, k, rot_dims, log2_base, c, s);
+            int a = interleaved ? 2 * k : k, b = interleaved ? 2 * k + 1 : k + half;
+            T *p = q + (size_t)t * q_stride + (size_t)hd * q_head_stride + q_first;
+            float u = to_f(p[a]), v = to_f(p[b]);
+            p[a] = from_f<T>(u * c - v * s);
+            p[b] = from_f<T>(v * c + u * s);
+        }
+    }
     int page = block_table[(size_t)tok_seq[t] * max_pages + pos / page_size];
     bool ok = page >= 0 && page < num_pages;  // a bad table entry drops the write instead of corrupting another page
     T *dst = slab + ((size_t)(ok ? page : 0) * page_size + pos % page_size) * width;
@@ -213,15 +227,25 @@ int tlb_rope_rows(void *x, long long row_stride, long long head_stride, int firs
 int tlb_latent_append(const void *down, const void *norm_w, float eps, int rank, int rot, int rot_dims, int interleaved, double base,
                       const int32_t *tok_pos, const int32_t *tok_seq, const int32_t *block_table, int max_pages, int num_pages, int page_size,
                       void *slab, int tokens, int dtype, void *stream) {
+    return tlb_latent_prepare(down, rank + rot, norm_w, eps, rank, rot, rot_dims, interleaved, base, tok_pos, tok_seq, block_table, max_pages, num_pages,
+                              page_size, slab, nullptr, 0, 0, 0, 0, tokens, dtype, stream);
+}
+
+int tlb_latent_prepare(const void *down, long long down_stride, const void *norm_w, float eps, int rank, int rot, int rot_dims, int interleaved,
+                       double base, const int32_t *tok_pos, const int32_t *tok_seq, const int32_t *block_table, int max_pages, int num_pages,
+                       int page_size, void *slab, void *q, long long q_stride, int q_heads, int q_head_stride, int q_first, int tokens, int dtype,
+                       void *stream) {
     if (tokens <= 0) return TL_OK;
     if (!down || !norm_w || !tok_pos || !tok_seq || !block_table || !slab || rank <= 0 || rot < 0 || rot_dims > rot || (rot_dims & 1) ||
         page_size <= 0 || max_pages <= 0 || base <= 0)
         return tl::fail(TL_EINVAL, "latent_append: bad argument");
+    if (q && (q_heads <= 0 || q_first < 0 || q_first + rot_dims > q_head_stride)) return tl::fail(TL_EINVAL, "latent_prepare: bad query layout");
     double lb = log2(base);
     TLB_DISPATCH(dtype, "latent_append",
                  latent_append_kernel<T><<<tokens, 128, 0, as_stream(stream)>>>((const T *)down, (const T *)norm_w, eps, rank, rot, rot_dims, interleaved,
                                                                                lb, tok_pos, tok_seq, block_table, max_pages, num_pages, page_size,
-                                                                               (T *)slab));
+                                                                               (T *)slab, down_stride, (T *)q, q_stride, q_heads, q_head_stride,
+                                                                               q_first));
     TL_LAUNCH_CHECK("latent_append");
     return TL_OK;
 }

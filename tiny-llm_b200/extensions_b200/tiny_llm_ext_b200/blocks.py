@@ -28,6 +28,7 @@ _SIGNATURES = {
     "tlb_norm_residual": (_I, [_VP, _I, _VP, _F, _VP, _F, _VP, _VP, _I, _I, _I, _VP]),
     "tlb_rope_rows": (_I, [_VP, _LL, _LL, _I, _I, _I, _I, _D, _VP, _I, _I, _VP]),
     "tlb_latent_append": (_I, [_VP, _VP, _F, _I, _I, _I, _I, _D, _VP, _VP, _VP, _I, _I, _I, _VP, _I, _I, _VP]),
+    "tlb_latent_prepare": (_I, [_VP, _LL, _VP, _F, _I, _I, _I, _I, _D, _VP, _VP, _VP, _I, _I, _I, _VP, _VP, _LL, _I, _I, _I, _I, _I, _VP]),
     "tlb_latent_attention": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _VP, _LL, _LL, _I, _VP]),
     "tlb_latent_attention_mma_tile_tokens": (_I, [_I]),
     "tlb_latent_attention_mma_supported": (_I, [_I, _I, _I]),
@@ -178,6 +179,22 @@ def latent_append(down, norm_weight, eps, *, rank, rot_dims, interleaved, base, 
     _check(library().tlb_latent_append(_ptr(down), _ptr(norm_weight), float(eps), rank, width - rank, rot_dims, int(interleaved), float(base),
                                        _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), block_table.shape[1], P, page_size, _ptr(slab), T,
                                        _code(down.dtype), _stream(down)))
+
+
+def latent_prepare(qd, norm_weight, eps, *, heads, dim, rot_dim, rank, rot_dims, interleaved, base, tok_pos, tok_seq, block_table, slab):
+    """One launch after a fused q|dkv projection ``qd [T, heads * (dim + rot_dim) + rank + rot_dim]``: rotate the rotated
+    part of every query head in place, norm the latent, rotate the shared key part and store both in ``slab``."""
+    _gpu("latent_prepare", qd, norm_weight, tok_pos, tok_seq, block_table, slab)
+    _contig("latent_prepare", qd, norm_weight, tok_pos, tok_seq, block_table, slab)
+    T, total = qd.shape
+    P, page_size, width = slab.shape
+    q_width = heads * (dim + rot_dim)
+    if total != q_width + width or width != rank + rot_dim or slab.dtype != qd.dtype or norm_weight.dtype != qd.dtype or norm_weight.numel() != rank:
+        raise RuntimeError("latent_prepare: projection, slab and weight do not match")
+    es = qd.element_size()
+    _check(library().tlb_latent_prepare(qd.data_ptr() + q_width * es, total, _ptr(norm_weight), float(eps), rank, rot_dim, rot_dims, int(interleaved),
+                                        float(base), _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), block_table.shape[1], P, page_size, _ptr(slab),
+                                        _ptr(qd), total, heads, dim + rot_dim, dim, T, _code(qd.dtype), _stream(qd)))
 
 
 def attention_kernel(dtype, heads: int, rank: int, rot: int, page_size: int) -> tuple[str, int]:

@@ -32,13 +32,15 @@ class LatentAttention:
             raise ValueError("latent attention: projection shapes do not match the head sizes")
         if rot_dims > rot_dim or rot_dims % 2:
             raise ValueError("latent attention: rotary dims must be even and fit the rotated part")
-        self.w_q, self.w_o = w_q.contiguous(), w_o.contiguous()
+        self.w_q, self.w_o = (None if w_dkv is not None else w_q.contiguous()), w_o.contiguous()
         self.w_uk = w_uk.reshape(heads, dim, kv_rank).contiguous()                    # q_lat_h = q_plain_h @ w_uk[h]
         self.w_uv_t = w_uv.reshape(heads, vdim, kv_rank).transpose(1, 2).contiguous()  # o_h = o_lat_h @ w_uv_t[h]
-        self.w_dkv = None if w_dkv is None else w_dkv.contiguous()
         self.dkv_norm = None if dkv_norm is None else dkv_norm.contiguous()
-        if self.w_dkv is not None and tuple(self.w_dkv.shape)[0] != kv_rank + rot_dim:
+        if w_dkv is not None and tuple(w_dkv.shape)[0] != kv_rank + rot_dim:
             raise ValueError("latent attention: the down projection must have kv_rank + rot_dim rows")
+        # a caching layer projects q and the latent in ONE product (rows of w_q, then rows of w_dkv)
+        self.caches = w_dkv is not None
+        self.w_qd = torch.cat([w_q, w_dkv], dim=0).contiguous() if self.caches else None
 
     @property
     def cache_width(self) -> int:
@@ -54,14 +56,17 @@ class LatentAttention:
         from extensions_b200.tiny_llm_ext_b200 import blocks
 
         T, H, dn, dr = h.shape[0], self.heads, self.dim, self.rot_dim
-        q = linear(h, self.w_q)
-        if self.w_dkv is not None:
-            blocks.latent_append(linear(h, self.w_dkv), self.dkv_norm, self.eps, rank=self.rank, rot_dims=self.rot_dims,
-                                 interleaved=self.interleaved, base=self.rot_base, tok_pos=plan.tok_pos, tok_seq=plan.tok_seq,
-                                 block_table=plan.block_table, slab=slab)
-        blocks.rope_rows(q, plan.tok_pos, heads=H, head_stride=dn + dr, first=dn, dims=self.rot_dims, base=self.rot_base, interleaved=self.interleaved)
+        if self.caches:
+            qd = linear(h, self.w_qd)  # [T, H (dn + dr) | rank + dr]
+            blocks.latent_prepare(qd, self.dkv_norm, self.eps, heads=H, dim=dn, rot_dim=dr, rank=self.rank, rot_dims=self.rot_dims,
+                                  interleaved=self.interleaved, base=self.rot_base, tok_pos=plan.tok_pos, tok_seq=plan.tok_seq,
+                                  block_table=plan.block_table, slab=slab)
+            q3 = qd[:, : H * (dn + dr)].unflatten(1, (H, dn + dr))
+        else:
+            q = linear(h, self.w_q)
+            blocks.rope_rows(q, plan.tok_pos, heads=H, head_stride=dn + dr, first=dn, dims=self.rot_dims, base=self.rot_base, interleaved=self.interleaved)
+            q3 = q.view(T, H, dn + dr)
         kernel, tile_tokens = self.attention_kernel(slab)
-        q3 = q.view(T, H, dn + dr)
         q_lat = torch.bmm(q3[:, :, :dn].transpose(0, 1), self.w_uk)          # [H, T, rank]
         o_lat = torch.empty_like(q_lat)
         blocks.latent_attention(q_lat.transpose(0, 1), q3[:, :, dn:], slab, plan.block_table, plan.tiles_for(tile_tokens), plan.tok_pos,
