@@ -882,7 +882,7 @@ def _voluzen_kernels(cfg: dict, device, prompt: int, batch: int, context: int) -
         q_lat = torch.randn((T, H, R), dtype=torch.float32, device=device).to(bf)
         q_rot = torch.randn((T, H, dr), dtype=torch.float32, device=device).to(bf)
         o = torch.empty_like(q_lat)
-        ms = timed(lambda: blocks.latent_attention(q_lat, q_rot, slab, table, tiles, pos, window=0, scale=0.05, out=o, kernel=kernel))
+        ms = timed(lambda: blocks.latent_attention(q_lat, q_rot, slab, table, tiles, pos, window=0, scale=0.05, out=o, kernel=kernel, max_context=ctx))
         return ms, slab.numel() * 2
 
     ms, _ = attention(prompt, 1, prompt)

@@ -95,21 +95,22 @@ int tlb_gated_act(const void *gu, void *out, int rows, int width, int act, int d
 int tlb_moe_route(const void *h, const void *w, const void *b, int tokens, int dim, int experts, int top, int32_t *idx, float *gate,
                   int dtype, void *stream);
 
-/* Rows per expert tile of the grouped products, and the sizes a caller has to provide. */
+/* Rows per expert tile of the grouped products: 32, or 64 for the tensor-core kernels (bf16, reduction length % 8 == 0)
+ * when experts get many rows (half the weight traffic per row). */
 #define TLB_MOE_TILE_ROWS 32
 /* upper bound of sorted rows (pairs grouped by expert, every group padded to whole tiles) */
-long long tlb_moe_max_rows(int tokens, int top, int experts);
-/* Group the (token, choice) pairs by expert: sorted_pair [max_rows] (pair id or -1), tile_expert [max_rows / TILE],
+long long tlb_moe_max_rows(int tokens, int top, int experts, int tile_rows);
+/* Group the (token, choice) pairs by expert: sorted_pair [max_rows] (pair id or -1), tile_expert [max_rows / tile_rows],
  * counters [2] = {tiles in use, rows in use}.  One launch, no host involvement. */
-int tlb_moe_sort(const int32_t *idx, int tokens, int top, int experts, int32_t *sorted_pair, int32_t *tile_expert, int32_t *counters,
-                 void *stream);
+int tlb_moe_sort(const int32_t *idx, int tokens, int top, int experts, int tile_rows, int32_t *sorted_pair, int32_t *tile_expert,
+                 int32_t *counters, void *stream);
 /* inter[row, :] = act(Wg[e] h[token(row)]) * (Wu[e] h[token(row)]); Wg, Wu [experts, ff, dim]; inter [max_rows, ff]. */
 int tlb_moe_gate_up(const void *h, const void *wg, const void *wu, const int32_t *sorted_pair, const int32_t *tile_expert,
-                    const int32_t *counters, int tokens, int top, int experts, int dim, int ff, int act, void *inter, int dtype,
-                    void *stream);
+                    const int32_t *counters, int tokens, int top, int experts, int tile_rows, int dim, int ff, int act, void *inter,
+                    int dtype, void *stream);
 /* pair_out[pair, :] = Wd[e] inter[row, :] (fp32); Wd [experts, dim, ff]. */
 int tlb_moe_down(const void *inter, const void *wd, const int32_t *sorted_pair, const int32_t *tile_expert, const int32_t *counters,
-                 int tokens, int top, int experts, int dim, int ff, float *pair_out, int dtype, void *stream);
+                 int tokens, int top, int experts, int tile_rows, int dim, int ff, float *pair_out, int dtype, void *stream);
 /* y[t,:] = sum_k gate[t,k] * pair_out[t*top+k,:] (+ shared[t,:] if shared != NULL, stored in `dtype`), fp32, in choice order. */
 int tlb_moe_combine(const float *pair_out, const float *gate, const void *shared, float *y, int tokens, int top, int dim, int dtype,
                     void *stream);

@@ -260,9 +260,10 @@ def test_fused_prepare_rotates_the_queries_and_fills_the_cache_in_one_launch(dev
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("experts,top,shared", [(6, 2, True), (5, 1, False), (4, 4, True), (40, 3, False)])
-def test_router_and_experts_against_the_loop_over_tokens(dev, dtype, experts, top, shared):
-    D, ff, T = 72, 40, 37
+@pytest.mark.parametrize("experts,top,shared,T", [(6, 2, True, 37), (5, 1, False, 37), (4, 4, True, 37), (40, 3, False, 37), (3, 2, True, 150)])
+def test_router_and_experts_against_the_loop_over_tokens(dev, dtype, experts, top, shared, T):
+    # (the last case gives every expert about 100 rows: the bf16 path then takes 64-row tiles)
+    D, ff = 72, 40
     g = torch.Generator().manual_seed(experts)
     w = {"router": torch.randn(experts, D, generator=g).to(dtype), "router.b": torch.randn(experts, generator=g).to(dtype)}
     for e in range(experts):

@@ -67,7 +67,7 @@ moe_route_kernel(const T *__restrict__ h, const T *__restrict__ w, const T *__re
 }
 
 // Single CTA: histogram, padded exclusive scan, scatter.
-__global__ void moe_sort_kernel(const int32_t *__restrict__ idx, int pairs, int experts, int max_rows, int32_t *__restrict__ sorted_pair,
+__global__ void moe_sort_kernel(const int32_t *__restrict__ idx, int pairs, int experts, int max_rows, int tile_rows, int32_t *__restrict__ sorted_pair,
                                 int32_t *__restrict__ tile_expert, int32_t *__restrict__ counters) {
     extern __shared__ int sm[];
     int *count = sm, *start = sm + experts, *cursor = sm + 2 * experts;
@@ -83,11 +83,11 @@ __global__ void moe_sort_kernel(const int32_t *__restrict__ idx, int pairs, int 
         int row = 0;
         for (int e = 0; e < experts; ++e) {
             start[e] = row;
-            int tiles = (count[e] + kTileRows - 1) / kTileRows;
-            for (int i = 0; i < tiles; ++i) tile_expert[row / kTileRows + i] = e;
-            row += tiles * kTileRows;
+            int tiles = (count[e] + tile_rows - 1) / tile_rows;
+            for (int i = 0; i < tiles; ++i) tile_expert[row / tile_rows + i] = e;
+            row += tiles * tile_rows;
         }
-        counters[0] = row / kTileRows;
+        counters[0] = row / tile_rows;
         counters[1] = row;
     }
     __syncthreads();
@@ -170,7 +170,7 @@ moe_grouped_kernel(const T *__restrict__ a, const T *__restrict__ w1, const T *_
 
 
 // ---- the grouped products on the tensor cores (bf16, K % 8 == 0) ------------------------------------------------
-// One CTA = one 32-row expert tile x 128 output columns; 8 warps = 2 row halves x 4 column quarters of 32, each
+// One CTA = one 32- or 64-row expert tile x 128 output columns; 8 warps = 2 row halves x 4 column quarters (4 x 2 for 64 rows), each
 // mma.sync m16n8k16 over 32-wide reduction blocks that cp.async brings into a two-stage ring (A rows gathered
 // through the sorted pair list).  fp32 accumulators; the reduction order of a row is k ascending in both kernels.
 constexpr int kTN = 128, kTK = 32, kTS = kTK + 8;  // row stride 40 elements = 80 B: (80 / 16) odd, conflict-free ldmatrix
@@ -190,19 +190,23 @@ __device__ __forceinline__ void moe_cp16(void *dst, const void *src, bool ok) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
 }
 
-template <bool GATED>
+template <bool GATED, int BM>
 __global__ void __launch_bounds__(256)
 moe_grouped_mma_kernel(const bf16 *__restrict__ a, const bf16 *__restrict__ w1, const bf16 *__restrict__ w2, const int32_t *__restrict__ sorted_pair,
                        const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ counters, int top, int K, int N, int act,
                        bf16 *__restrict__ inter, float *__restrict__ pair_out) {
     if ((int)blockIdx.x >= counters[0]) return;
-    __shared__ __align__(16) bf16 sa[2][kTileRows * kTS];
-    __shared__ __align__(16) bf16 sb1[2][kTN * kTS];
-    __shared__ __align__(16) bf16 sb2[GATED ? 2 : 1][GATED ? kTN * kTS : 8];
-    __shared__ int src_row[kTileRows];
+    constexpr int MT = BM / 16;          // 16-row halves/quarters of the tile
+    constexpr int NW = 8 / MT;           // warps along the columns
+    constexpr int NPW = kTN / NW / 8;    // 8-column blocks per warp
+    extern __shared__ __align__(16) unsigned char moe_smem[];
+    bf16 (*sa)[BM * kTS] = reinterpret_cast<bf16 (*)[BM * kTS]>(moe_smem);                              // [2]
+    bf16 (*sb1)[kTN * kTS] = reinterpret_cast<bf16 (*)[kTN * kTS]>(moe_smem + 2 * BM * kTS * 2);        // [2]
+    bf16 (*sb2)[kTN * kTS] = reinterpret_cast<bf16 (*)[kTN * kTS]>(moe_smem + 2 * (BM + kTN) * kTS * 2);  // [2], gated only
+    __shared__ int src_row[BM];
     const int e = tile_expert[blockIdx.x];
-    const int row0 = blockIdx.x * kTileRows, col0 = blockIdx.y * kTN;
-    if (threadIdx.x < kTileRows) {
+    const int row0 = blockIdx.x * BM, col0 = blockIdx.y * kTN;
+    if (threadIdx.x < BM) {
         int pair = sorted_pair[row0 + threadIdx.x];
         src_row[threadIdx.x] = pair < 0 ? -1 : (GATED ? pair / top : row0 + (int)threadIdx.x);
     }
@@ -210,11 +214,11 @@ moe_grouped_mma_kernel(const bf16 *__restrict__ a, const bf16 *__restrict__ w1, 
     const bf16 *wa = w1 + (size_t)e * N * K;
     const bf16 *wb = GATED ? w2 + (size_t)e * N * K : nullptr;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int mt = warp & 1, nq = warp >> 1;
+    const int mt = warp % MT, nq = warp / MT;
 
     auto stage = [&](int kb, int buf) {
         int k0 = kb * kTK;
-        if (threadIdx.x < kTileRows * 4) {  // A: 32 rows x 4 pieces of 8
+        if (threadIdx.x < BM * 4) {  // A: BM rows x 4 pieces of 8
             int r = threadIdx.x >> 2, piece = threadIdx.x & 3;
             int sr = src_row[r], k = k0 + piece * 8;
             bool ok = sr >= 0 && k < K;
@@ -231,7 +235,7 @@ moe_grouped_mma_kernel(const bf16 *__restrict__ a, const bf16 *__restrict__ w1, 
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
-    float c1[4][4] = {}, c2[GATED ? 4 : 1][4] = {};
+    float c1[NPW][4] = {}, c2[GATED ? NPW : 1][4] = {};
     const int kblocks = (K + kTK - 1) / kTK;
     stage(0, 0);
     for (int kb = 0; kb < kblocks; ++kb) {
@@ -244,8 +248,8 @@ moe_grouped_mma_kernel(const bf16 *__restrict__ a, const bf16 *__restrict__ w1, 
             uint32_t a0, a1, a2, a3;
             moe_ldm_x4(a0, a1, a2, a3, &sa[buf][(mt * 16 + (lane & 15)) * kTS + ks * 16 + (lane >> 4) * 8]);
 #pragma unroll
-            for (int np = 0; np < 2; ++np) {  // two n8 tiles per ldmatrix.x4: rows n..n+7 and n+8..n+15, k halves 0 / 8
-                int n = nq * 32 + np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8;
+            for (int np = 0; np < NPW / 2; ++np) {  // two n8 tiles per ldmatrix.x4: rows n..n+7 and n+8..n+15, k halves 0 / 8
+                int n = nq * (8 * NPW) + np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8;
                 int kk = ks * 16 + ((lane >> 3) & 1) * 8;
                 uint32_t b0, b1, b2, b3;
                 moe_ldm_x4(b0, b1, b2, b3, &sb1[buf][n * kTS + kk]);
@@ -266,10 +270,10 @@ moe_grouped_mma_kernel(const bf16 *__restrict__ a, const bf16 *__restrict__ w1, 
         int pair = sorted_pair[row];
         if (pair < 0) continue;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < NPW; ++i) {
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-                int col = col0 + nq * 32 + i * 8 + 2 * t + j;
+                int col = col0 + nq * (8 * NPW) + i * 8 + 2 * t + j;
                 if (col >= N) continue;
                 float v = c1[i][half * 2 + j];
                 if (GATED) inter[(size_t)row * N + col] = __float2bfloat16_rn(moe_act(v, act) * c2[i][half * 2 + j]);
@@ -295,6 +299,23 @@ __global__ void moe_combine_kernel(const float *__restrict__ pair_out, const flo
 
 using namespace tlb;
 
+template <bool GATED, int BM>
+static int launch_grouped_mma(dim3 grid, cudaStream_t st, const bf16 *a, const bf16 *w1, const bf16 *w2, const int32_t *sorted_pair,
+                              const int32_t *tile_expert, const int32_t *counters, int top, int K, int N, int act, bf16 *inter, float *pair_out) {
+    size_t smem = (size_t)2 * (BM + kTN * (GATED ? 2 : 1)) * kTS * sizeof(bf16);
+    auto kernel = moe_grouped_mma_kernel<GATED, BM>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return tl::fail(TL_ECUDA, "moe_grouped: %s", cudaGetErrorString(e));
+    }
+    kernel<<<grid, 256, smem, st>>>(a, w1, w2, sorted_pair, tile_expert, counters, top, K, N, act, inter, pair_out);
+    return TL_OK;
+}
+
+static bool moe_mma_ok(int dtype, int k, const void *a, const void *w1, const void *w2) {
+    return dtype == TL_BF16 && k % 8 == 0 && tl::aligned16(a) && tl::aligned16(w1) && (!w2 || tl::aligned16(w2));
+}
+
 extern "C" {
 
 int tlb_moe_route(const void *h, const void *w, const void *b, int tokens, int dim, int experts, int top, int32_t *idx, float *gate, int dtype,
@@ -310,38 +331,45 @@ int tlb_moe_route(const void *h, const void *w, const void *b, int tokens, int d
     return TL_OK;
 }
 
-long long tlb_moe_max_rows(int tokens, int top, int experts) {
+long long tlb_moe_max_rows(int tokens, int top, int experts, int tile_rows) {
     long long pairs = (long long)tokens * top;
     long long groups = pairs < experts ? pairs : experts;  // at most min(pairs, experts) groups carry padding
-    long long rows = pairs + groups * (kTileRows - 1);
-    return (rows + kTileRows - 1) / kTileRows * kTileRows;
+    long long rows = pairs + groups * (tile_rows - 1);
+    return (rows + tile_rows - 1) / tile_rows * tile_rows;
 }
 
-int tlb_moe_sort(const int32_t *idx, int tokens, int top, int experts, int32_t *sorted_pair, int32_t *tile_expert, int32_t *counters,
-                 void *stream) {
+int tlb_moe_sort(const int32_t *idx, int tokens, int top, int experts, int tile_rows, int32_t *sorted_pair, int32_t *tile_expert,
+                 int32_t *counters, void *stream) {
     if (tokens <= 0) return TL_OK;
-    if (!idx || !sorted_pair || !tile_expert || !counters || top <= 0 || experts <= 0) return tl::fail(TL_EINVAL, "moe_sort: bad argument");
+    if (!idx || !sorted_pair || !tile_expert || !counters || top <= 0 || experts <= 0 || (tile_rows != 32 && tile_rows != 64))
+        return tl::fail(TL_EINVAL, "moe_sort: bad argument");
     size_t smem = (size_t)3 * experts * sizeof(int);
     if (smem > 48 * 1024) return tl::fail(TL_EINVAL, "moe_sort: %d experts do not fit", experts);
-    moe_sort_kernel<<<1, 1024, smem, as_stream(stream)>>>(idx, tokens * top, experts, (int)tlb_moe_max_rows(tokens, top, experts), sorted_pair,
-                                                          tile_expert, counters);
+    moe_sort_kernel<<<1, 1024, smem, as_stream(stream)>>>(idx, tokens * top, experts, (int)tlb_moe_max_rows(tokens, top, experts, tile_rows), tile_rows,
+                                                          sorted_pair, tile_expert, counters);
     TL_LAUNCH_CHECK("moe_sort");
     return TL_OK;
 }
 
+// The tensor-core kernels take 32- or 64-row expert tiles (64 halves the weight traffic per row when experts get many
+// rows); the fp32 kernels 32 only.
 int tlb_moe_gate_up(const void *h, const void *wg, const void *wu, const int32_t *sorted_pair, const int32_t *tile_expert, const int32_t *counters,
-                    int tokens, int top, int experts, int dim, int ff, int act, void *inter, int dtype, void *stream) {
+                    int tokens, int top, int experts, int tile_rows, int dim, int ff, int act, void *inter, int dtype, void *stream) {
     if (tokens <= 0) return TL_OK;
     if (!h || !wg || !wu || !sorted_pair || !tile_expert || !counters || !inter || dim <= 0 || ff <= 0 || top <= 0)
         return tl::fail(TL_EINVAL, "moe_gate_up: bad argument");
-    if (dtype == TL_BF16 && dim % 8 == 0 && tl::aligned16(h) && tl::aligned16(wg) && tl::aligned16(wu)) {
-        dim3 tc((unsigned)(tlb_moe_max_rows(tokens, top, experts) / kTileRows), ceil_div(ff, kTN));
-        moe_grouped_mma_kernel<true><<<tc, 256, 0, as_stream(stream)>>>((const bf16 *)h, (const bf16 *)wg, (const bf16 *)wu, sorted_pair, tile_expert,
-                                                                        counters, top, dim, ff, act, (bf16 *)inter, nullptr);
+    if (moe_mma_ok(dtype, dim, h, wg, wu)) {
+        dim3 tc((unsigned)(tlb_moe_max_rows(tokens, top, experts, tile_rows) / tile_rows), ceil_div(ff, kTN));
+        int rc = tile_rows == 64 ? launch_grouped_mma<true, 64>(tc, as_stream(stream), (const bf16 *)h, (const bf16 *)wg, (const bf16 *)wu, sorted_pair,
+                                                                tile_expert, counters, top, dim, ff, act, (bf16 *)inter, nullptr)
+                                 : launch_grouped_mma<true, 32>(tc, as_stream(stream), (const bf16 *)h, (const bf16 *)wg, (const bf16 *)wu, sorted_pair,
+                                                                tile_expert, counters, top, dim, ff, act, (bf16 *)inter, nullptr);
+        if (rc != TL_OK) return rc;
         TL_LAUNCH_CHECK("moe_gate_up");
         return TL_OK;
     }
-    dim3 grid((unsigned)(tlb_moe_max_rows(tokens, top, experts) / kTileRows), ceil_div(ff, kBN));
+    if (tile_rows != kTileRows) return tl::fail(TL_EINVAL, "moe_gate_up: %d-row tiles need the tensor-core kernel", tile_rows);
+    dim3 grid((unsigned)(tlb_moe_max_rows(tokens, top, experts, kTileRows) / kTileRows), ceil_div(ff, kBN));
     TLB_DISPATCH(dtype, "moe_gate_up",
                  moe_grouped_kernel<T, true><<<grid, 256, 0, as_stream(stream)>>>((const T *)h, (const T *)wg, (const T *)wu, sorted_pair, tile_expert,
                                                                                  counters, top, dim, ff, act, (T *)inter, nullptr));
@@ -350,18 +378,22 @@ int tlb_moe_gate_up(const void *h, const void *wg, const void *wu, const int32_t
 }
 
 int tlb_moe_down(const void *inter, const void *wd, const int32_t *sorted_pair, const int32_t *tile_expert, const int32_t *counters, int tokens,
-                 int top, int experts, int dim, int ff, float *pair_out, int dtype, void *stream) {
+                 int top, int experts, int tile_rows, int dim, int ff, float *pair_out, int dtype, void *stream) {
     if (tokens <= 0) return TL_OK;
     if (!inter || !wd || !sorted_pair || !tile_expert || !counters || !pair_out || dim <= 0 || ff <= 0 || top <= 0)
         return tl::fail(TL_EINVAL, "moe_down: bad argument");
-    if (dtype == TL_BF16 && ff % 8 == 0 && tl::aligned16(inter) && tl::aligned16(wd)) {
-        dim3 tc((unsigned)(tlb_moe_max_rows(tokens, top, experts) / kTileRows), ceil_div(dim, kTN));
-        moe_grouped_mma_kernel<false><<<tc, 256, 0, as_stream(stream)>>>((const bf16 *)inter, (const bf16 *)wd, nullptr, sorted_pair, tile_expert,
-                                                                         counters, top, ff, dim, 0, nullptr, pair_out);
+    if (moe_mma_ok(dtype, ff, inter, wd, nullptr)) {
+        dim3 tc((unsigned)(tlb_moe_max_rows(tokens, top, experts, tile_rows) / tile_rows), ceil_div(dim, kTN));
+        int rc = tile_rows == 64 ? launch_grouped_mma<false, 64>(tc, as_stream(stream), (const bf16 *)inter, (const bf16 *)wd, nullptr, sorted_pair,
+                                                                 tile_expert, counters, top, ff, dim, 0, nullptr, pair_out)
+                                 : launch_grouped_mma<false, 32>(tc, as_stream(stream), (const bf16 *)inter, (const bf16 *)wd, nullptr, sorted_pair,
+                                                                 tile_expert, counters, top, ff, dim, 0, nullptr, pair_out);
+        if (rc != TL_OK) return rc;
         TL_LAUNCH_CHECK("moe_down");
         return TL_OK;
     }
-    dim3 grid((unsigned)(tlb_moe_max_rows(tokens, top, experts) / kTileRows), ceil_div(dim, kBN));
+    if (tile_rows != kTileRows) return tl::fail(TL_EINVAL, "moe_down: %d-row tiles need the tensor-core kernel", tile_rows);
+    dim3 grid((unsigned)(tlb_moe_max_rows(tokens, top, experts, kTileRows) / kTileRows), ceil_div(dim, kBN));
     TLB_DISPATCH(dtype, "moe_down",
                  moe_grouped_kernel<T, false><<<grid, 256, 0, as_stream(stream)>>>((const T *)inter, (const T *)wd, nullptr, sorted_pair, tile_expert,
                                                                                   counters, top, ff, dim, 0, nullptr, pair_out));

@@ -44,26 +44,79 @@ __global__ void embed_rows_kernel(const int32_t *__restrict__ ids, const T *__re
     }
 }
 
-template <typename T, typename TY>
+// 4 consecutive elements of a row as floats (one 8- or 16-byte access)
+__device__ __forceinline__ float4 load4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+__device__ __forceinline__ float4 load4(const bf16 *p) {
+    uint2 u = *reinterpret_cast<const uint2 *>(p);
+    float2 a = tl::unpack2<bf16>(u.x), b = tl::unpack2<bf16>(u.y);
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+__device__ __forceinline__ void store4(bf16 *p, float4 v) {
+    *reinterpret_cast<uint2 *>(p) = make_uint2(tl::pack2<bf16>(v.x, v.y), tl::pack2<bf16>(v.z, v.w));
+}
+
+// VEC: rows are read and written 4 elements at a time (dim % 4 == 0, 16-byte aligned bases); the row's values stay in
+// registers between the two passes when it has at most 4 * KEEP * blockDim elements.
+template <typename T, typename TY, bool VEC>
 __global__ void norm_residual_kernel(const TY *__restrict__ y, const T *__restrict__ w, float weight_offset, const T *__restrict__ scale,
                                      float eps, float *__restrict__ residual, T *__restrict__ h, int dim) {
     __shared__ float scratch[33];
     size_t base = (size_t)blockIdx.x * dim;
     float ss = 0.f;
-    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-        float v = to_f(y[base + d]);
-        ss += v * v;
-    }
-    ss = block_sum(ss, scratch);
-    float inv = 1.0f / sqrtf(ss / (float)dim + eps);
-    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-        float n = to_f(y[base + d]) * inv * (to_f(w[d]) + weight_offset);
-        if (scale) n *= to_f(scale[d]);
-        if (residual) {
-            n += residual[base + d];
-            residual[base + d] = n;
+    if constexpr (VEC) {
+        constexpr int KEEP = 4;
+        float4 kept[KEEP];
+        const int quads = dim / 4;
+#pragma unroll
+        for (int i = 0; i < KEEP; ++i) {
+            int q = threadIdx.x + i * blockDim.x;
+            kept[i] = q < quads ? load4(y + base + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
+            ss += kept[i].x * kept[i].x + kept[i].y * kept[i].y + kept[i].z * kept[i].z + kept[i].w * kept[i].w;
         }
-        if (h) h[base + d] = from_f<T>(n);
+        for (int q = threadIdx.x + KEEP * blockDim.x; q < quads; q += blockDim.x) {
+            float4 v = load4(y + base + 4 * q);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = block_sum(ss, scratch);
+        float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+        auto finish = [&](int q, float4 v) {
+            float4 g = load4(w + 4 * q);
+            float4 n = make_float4(v.x * inv * (g.x + weight_offset), v.y * inv * (g.y + weight_offset), v.z * inv * (g.z + weight_offset),
+                                   v.w * inv * (g.w + weight_offset));
+            if (scale) {
+                float4 sc = load4(scale + 4 * q);
+                n.x *= sc.x, n.y *= sc.y, n.z *= sc.z, n.w *= sc.w;
+            }
+            if (residual) {
+                float4 r = load4(residual + base + 4 * q);
+                n.x += r.x, n.y += r.y, n.z += r.z, n.w += r.w;
+                store4(residual + base + 4 * q, n);
+            }
+            if (h) store4(h + base + 4 * q, n);
+        };
+#pragma unroll
+        for (int i = 0; i < KEEP; ++i) {
+            int q = threadIdx.x + i * blockDim.x;
+            if (q < quads) finish(q, kept[i]);
+        }
+        for (int q = threadIdx.x + KEEP * blockDim.x; q < quads; q += blockDim.x) finish(q, load4(y + base + 4 * q));
+    } else {
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+            float v = to_f(y[base + d]);
+            ss += v * v;
+        }
+        ss = block_sum(ss, scratch);
+        float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+            float n = to_f(y[base + d]) * inv * (to_f(w[d]) + weight_offset);
+            if (scale) n *= to_f(scale[d]);
+            if (residual) {
+                n += residual[base + d];
+                residual[base + d] = n;
+            }
+            if (h) h[base + d] = from_f<T>(n);
+        }
     }
 }
 
@@ -186,7 +239,7 @@ using namespace tlb;
 
 extern "C" {
 
-int tlb_abi_version(void) { return 1; }
+int tlb_abi_version(void) { return 2; }
 const char *tlb_last_error(void) { return tl::g_error; }
 long long tlb_launch_count(void) { return tl::g_launches.load(std::memory_order_relaxed); }
 
@@ -203,12 +256,16 @@ int tlb_norm_residual(const void *y, int y_is_f32, const void *w, float weight_o
                       int rows, int dim, int dtype, void *stream) {
     if (rows <= 0) return TL_OK;
     if (!y || !w || dim <= 0 || (!residual && !h)) return tl::fail(TL_EINVAL, "norm_residual: bad argument");
-    int threads = dim >= 1024 ? 512 : 256;
+    bool vec = dim % 4 == 0 && tl::aligned16(y) && tl::aligned16(w) && (!scale || tl::aligned16(scale)) && (!residual || tl::aligned16(residual)) &&
+               (!h || tl::aligned16(h));
+    int threads = dim >= 2048 ? 256 : 128;
+    cudaStream_t st = as_stream(stream);
+#define TLB_NORM(TY, V)                                                                                                                        \
+    norm_residual_kernel<T, TY, V><<<rows, threads, 0, st>>>((const TY *)y, (const T *)w, weight_offset, (const T *)scale, eps, residual, (T *)h, dim)
     TLB_DISPATCH(dtype, "norm_residual",
-                 if (y_is_f32) norm_residual_kernel<T, float><<<rows, threads, 0, as_stream(stream)>>>((const float *)y, (const T *)w, weight_offset,
-                                                                                                        (const T *)scale, eps, residual, (T *)h, dim);
-                 else norm_residual_kernel<T, T><<<rows, threads, 0, as_stream(stream)>>>((const T *)y, (const T *)w, weight_offset, (const T *)scale,
-                                                                                         eps, residual, (T *)h, dim));
+                 if (y_is_f32) { if (vec) TLB_NORM(float, true); else TLB_NORM(float, false); }
+                 else { if (vec) TLB_NORM(T, true); else TLB_NORM(T, false); });
+#undef TLB_NORM
     TL_LAUNCH_CHECK("norm_residual");
     return TL_OK;
 }

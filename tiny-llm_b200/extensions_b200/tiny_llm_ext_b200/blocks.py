@@ -37,15 +37,16 @@ _SIGNATURES = {
     "tlb_latent_attention_mma_workspace": (ctypes.c_size_t, [_I, _I, _I, _I]),
     "tlb_gated_act": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
     "tlb_moe_route": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _VP, _VP, _I, _VP]),
-    "tlb_moe_max_rows": (_LL, [_I, _I, _I]),
-    "tlb_moe_sort": (_I, [_VP, _I, _I, _I, _VP, _VP, _VP, _VP]),
-    "tlb_moe_gate_up": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _VP, _I, _VP]),
-    "tlb_moe_down": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _I, _VP]),
+    "tlb_moe_max_rows": (_LL, [_I, _I, _I, _I]),
+    "tlb_moe_sort": (_I, [_VP, _I, _I, _I, _I, _VP, _VP, _VP, _VP]),
+    "tlb_moe_gate_up": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _VP, _I, _VP]),
+    "tlb_moe_down": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _VP, _I, _VP]),
     "tlb_moe_combine": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _VP]),
     "tlb_argmax_rows": (_I, [_VP, _VP, _I, _I, _VP]),
 }
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
 
+ABI_VERSION = 2
 ATTENTION_TILE_TOKENS = 4
 MOE_TILE_ROWS = 32
 ACT_SILU, ACT_GELU_TANH = 0, 1
@@ -72,6 +73,18 @@ def load_library(path: str | os.PathLike | None = None) -> None:
         except Exception as exc:  # no nvcc, read-only tree, compile error
             raise ImportError(f"{candidate} is not built and could not be compiled: {exc}") from exc
     lib = ctypes.CDLL(str(candidate))
+    lib.tlb_abi_version.restype = _I
+    if lib.tlb_abi_version() != ABI_VERSION:  # a library built from other sources: calling it with these signatures would crash
+        if path is not None:
+            raise ImportError(f"{candidate} has ABI {lib.tlb_abi_version()}, this binding needs {ABI_VERSION}")
+        try:
+            candidate = _build()
+        except Exception as exc:
+            raise ImportError(f"{candidate} is out of date and could not be rebuilt: {exc}") from exc
+        lib = ctypes.CDLL(str(candidate))
+        lib.tlb_abi_version.restype = _I
+        if lib.tlb_abi_version() != ABI_VERSION:
+            raise ImportError(f"{candidate} has ABI {lib.tlb_abi_version()}, this binding needs {ABI_VERSION}")
     for name, (restype, argtypes) in _SIGNATURES.items():
         fn = getattr(lib, name)
         fn.restype = restype
@@ -290,18 +303,20 @@ def moe_experts(h, idx, gate, w_gate, w_up, w_down, act: int, shared=None) -> to
     T, D = h.shape
     E, ff, _ = w_gate.shape
     top = idx.shape[1]
-    max_rows = int(lib.tlb_moe_max_rows(T, top, E))
+    # 64-row expert tiles once the average expert gets that many rows (tensor-core kernels only: bf16, widths % 8 == 0)
+    rows = 64 if (h.dtype == torch.bfloat16 and D % 8 == 0 and ff % 8 == 0 and T * top >= 64 * E) else MOE_TILE_ROWS
+    max_rows = int(lib.tlb_moe_max_rows(T, top, E, rows))
     dev, code, st = h.device, _code(h.dtype), _stream(h)
     sorted_pair = torch.empty(max_rows, dtype=torch.int32, device=dev)
-    tile_expert = torch.empty(max_rows // MOE_TILE_ROWS, dtype=torch.int32, device=dev)
+    tile_expert = torch.empty(max_rows // rows, dtype=torch.int32, device=dev)
     counters = torch.empty(2, dtype=torch.int32, device=dev)
     inter = torch.empty((max_rows, ff), dtype=h.dtype, device=dev)
     pair_out = torch.empty((T * top, D), dtype=torch.float32, device=dev)
     y = torch.empty((T, D), dtype=torch.float32, device=dev)
-    _check(lib.tlb_moe_sort(_ptr(idx), T, top, E, _ptr(sorted_pair), _ptr(tile_expert), _ptr(counters), st))
-    _check(lib.tlb_moe_gate_up(_ptr(h), _ptr(w_gate), _ptr(w_up), _ptr(sorted_pair), _ptr(tile_expert), _ptr(counters), T, top, E, D, ff, act,
+    _check(lib.tlb_moe_sort(_ptr(idx), T, top, E, rows, _ptr(sorted_pair), _ptr(tile_expert), _ptr(counters), st))
+    _check(lib.tlb_moe_gate_up(_ptr(h), _ptr(w_gate), _ptr(w_up), _ptr(sorted_pair), _ptr(tile_expert), _ptr(counters), T, top, E, rows, D, ff, act,
                                _ptr(inter), code, st))
-    _check(lib.tlb_moe_down(_ptr(inter), _ptr(w_down), _ptr(sorted_pair), _ptr(tile_expert), _ptr(counters), T, top, E, D, ff, _ptr(pair_out), code, st))
+    _check(lib.tlb_moe_down(_ptr(inter), _ptr(w_down), _ptr(sorted_pair), _ptr(tile_expert), _ptr(counters), T, top, E, rows, D, ff, _ptr(pair_out), code, st))
     _check(lib.tlb_moe_combine(_ptr(pair_out), _ptr(gate), _ptr(shared), _ptr(y), T, top, D, code, st))
     return y
 
