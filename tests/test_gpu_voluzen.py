@@ -155,7 +155,7 @@ def run_attention(dev, dtype, q_full, rows, positions, rank, window, scale, page
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("rank,rot,heads", [(32, 8, 2), (96, 16, 4), (130, 6, 5), (512, 64, 3)])
+@pytest.mark.parametrize("rank,rot,heads", [(32, 8, 2), (96, 16, 4), (130, 6, 5), (33, 6, 3), (512, 64, 3)])
 def test_latent_attention_against_plain_attention(dev, dtype, rank, rot, heads):
     g = torch.Generator().manual_seed(rank)
     S = 150
@@ -168,7 +168,7 @@ def test_latent_attention_against_plain_attention(dev, dtype, rank, rot, heads):
         close(got, want, 2e-6 if dtype == torch.float32 else 1.5e-2)
 
 
-@pytest.mark.parametrize("rank,rot,heads", [(32, 8, 1), (96, 16, 4), (130, 6, 5), (64, 32, 16), (256, 64, 40), (512, 64, 3)])
+@pytest.mark.parametrize("rank,rot,heads", [(32, 8, 1), (96, 16, 4), (130, 6, 5), (64, 32, 16), (256, 64, 40), (64, 8, 70), (512, 64, 3)])
 def test_tensor_core_attention_against_plain_attention_and_the_general_kernel(dev, rank, rot, heads):
     g = torch.Generator().manual_seed(rank + heads)
     S = 520
@@ -492,3 +492,26 @@ def test_trace_program_replays_steps_and_writes_logits(dev, tmp_path):
     assert row_error(got, torch.stack([wa[66], wa[69], wb[8]])) < 2e-5
     got = torch.from_numpy(np.fromfile(tmp_path / "out" / "2.f32", dtype="<f4").reshape(1, 97))
     assert row_error(got, wb[:1]) < 2e-5
+
+
+def test_command_line_generates_and_batches(dev, tmp_path, capsys):
+    """The two front doors on a checkpoint directory of this design: `generate` prints the plain model's greedy tokens,
+    `batch` serves three prompts through two slots."""
+    from tiny_llm_b200 import cli
+
+    config = voluzen_config(**CONFIGS["equal"])
+    tensors = synthetic_voluzen(config, seed=8)
+    save_voluzen(config, tensors, tmp_path / "ckpt")
+    prompt = ids_for(11, 97, 5)
+    want = O.greedy(config, tensors, prompt, 6)
+    assert cli.main(["generate", "--model", str(tmp_path / "ckpt"), "--dtype", "float32", "--prompt-ids", ",".join(map(str, prompt)),
+                     "--max-new-tokens", "6"]) == 0
+    assert [int(t) for t in capsys.readouterr().out.split()] == want
+    assert cli.main(["batch", "--model", str(tmp_path / "ckpt"), "--dtype", "float32", "--quiet", "--batch-size", "2", "--prefill-step", "4",
+                     "--max-new-tokens", "6", "--prompt-ids", ";".join(",".join(map(str, ids_for(n, 97, n))) for n in (11, 3, 7))]) == 0
+    out = capsys.readouterr().out
+    assert out.count("--- request") == 3
+    first = out.split("--- request 0\n")[1].split("\n")[0]
+    assert [int(t) for t in first.split()] == O.greedy(config, tensors, ids_for(11, 97, 11), 6)
+    assert cli.main(["generate", "--synthetic", "voluzen:WCS", "--prompt-ids", "5,17,3", "--max-new-tokens", "4"]) == 0
+    assert len(capsys.readouterr().out.split()) == 4

@@ -253,7 +253,8 @@ def latent_attention(q_lat, q_rot, slab, block_table, tiles, tok_pos, *, window:
         if slab.dtype != torch.bfloat16:
             raise RuntimeError("latent_attention: the tensor-core kernel takes a bfloat16 cache")
         reach = min(max_context, int(window)) if window else max_context  # keys a query can see at most
-        splits = attention_splits(tiles.shape[0] * -(-H // 32), reach, slab.device) if reach else 1
+        rows = int(lib.tlb_latent_attention_mma_tile_tokens(1))  # query rows per CTA
+        splits = attention_splits(tiles.shape[0] * -(-H // rows), reach, slab.device) if reach else 1
         nbytes = int(lib.tlb_latent_attention_mma_workspace(tiles.shape[0], H, rank, splits))
         ws = torch.empty(nbytes, dtype=torch.uint8, device=slab.device) if nbytes else None
         _check(lib.tlb_latent_attention_mma(_ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(slab), P,
