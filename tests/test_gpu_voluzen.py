@@ -290,6 +290,9 @@ CONFIGS = {
     # head, top = 1), the third has sizes that are not multiples of anything convenient and a window of one page
     "mixed": dict(pattern="WCSMw", width=96, vocab=160, heads=2, dim=16, rot_dim=8, vdim=24, kv_rank=40, window=24, experts=6, top=2),
     "equal": dict(pattern="cWSN", width=64, vocab=97, heads=1, dim=16, rot_dim=16, vdim=16, kv_rank=32, window=5, experts=3, top=1, ff=64),
+    # nothing is a multiple of 8: the general attention kernel and the FMA expert products serve bfloat16 too
+    "awkward": dict(pattern="CwSWcM", width=100, vocab=301, heads=3, dim=20, rot_dim=6, vdim=12, kv_rank=37, window=7, experts=5, top=3,
+                    expert_ff=20, shared_ff=28, ff=52),
     "odd": dict(pattern="wMCS", width=80, vocab=131, heads=5, dim=12, rot_dim=6, vdim=10, kv_rank=34, window=64, experts=7, top=7, expert_ff=24, shared_ff=0),
 }
 _models = {}

@@ -256,7 +256,8 @@ _F32_OUT = {"ok": None}
 
 
 def _linear_f32(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """``h @ w.T`` with the fp32 accumulator handed back unrounded (logits), where the library product can."""
+    """``h @ w.T`` with the fp32 accumulator handed back unrounded (logits), where the library product can do that for
+    these shapes; else the product in the compute dtype, widened."""
     if h.dtype == torch.float32:
         return linear(h, w)
     if _F32_OUT["ok"] is not False:
@@ -265,7 +266,6 @@ def _linear_f32(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
             _F32_OUT["ok"] = True
             return out
         except (TypeError, RuntimeError):
-            if _F32_OUT["ok"]:
-                raise
-            _F32_OUT["ok"] = False
+            if _F32_OUT["ok"] is None:
+                _F32_OUT["ok"] = False  # this torch has no such product at all
     return linear(h, w).float()
