@@ -32,6 +32,9 @@ Numbers on the JSON line (decode):
             decode graph issues them (2.137 GB of packed weights, > L2), replayed from a CUDA graph,
             CUDA-event timed; achieved = algorithmic bytes / time, traffic = ncu DRAM bytes of the same
             launches (read from the committed capture named in `traffic_source`, null if there is none)
+  --workload voluzen  (not a BASELINE config) the Voluzen design - latent attention + mixture of experts, bf16 weights - at
+            two sizes beside Qwen3 W4A16 of equal width / depth / heads / active feed-forward width: prefill and decode tok/s,
+            and the design's kernels alone against the measured peaks; its own JSON line
   cpu_baseline  the reference's CPU path (oracle.model: dense bf16 weights, readable operators) on the
             host cores, bounded sample
 """

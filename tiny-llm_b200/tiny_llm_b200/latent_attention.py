@@ -18,7 +18,7 @@ from __future__ import annotations
 
 import torch
 
-from .basics import linear
+from .basics import linear, linear_wide
 
 
 class LatentAttention:
@@ -73,4 +73,4 @@ class LatentAttention:
                                 window=self.window, scale=self.scale, out=o_lat.transpose(0, 1), kernel=kernel,
                                 max_context=getattr(plan, "max_context", 0))
         o = torch.bmm(o_lat, self.w_uv_t)                                     # [H, T, vdim]
-        return linear(o.transpose(0, 1).reshape(T, H * self.vdim), self.w_o)
+        return linear_wide(o.transpose(0, 1).reshape(T, H * self.vdim), self.w_o)  # fp32: the layer's norm reads it unrounded

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import torch
 
-from .basics import linear
+from .basics import linear, linear_wide
 
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
 
@@ -22,10 +22,11 @@ class GatedMLP:
         self.w_down = w_down.contiguous()
         self.act = ACTIVATIONS[act]
 
-    def __call__(self, h: torch.Tensor) -> torch.Tensor:
+    def __call__(self, h: torch.Tensor, wide: bool = False) -> torch.Tensor:
+        """``wide``: hand the down projection's fp32 accumulator back unrounded (when a norm reads it next)."""
         from extensions_b200.tiny_llm_ext_b200 import blocks
 
-        return linear(blocks.gated_act(linear(h, self.w_gate_up), self.act), self.w_down)
+        return (linear_wide if wide else linear)(blocks.gated_act(linear(h, self.w_gate_up), self.act), self.w_down)
 
 
 class TopKRouter:

@@ -25,7 +25,7 @@ import torch
 
 from extensions_b200.tiny_llm_ext_b200 import blocks
 
-from .basics import linear
+from .basics import linear_wide
 from .kv_cache import BatchingKvCache
 from .latent_attention import LatentAttention
 from .latent_kv_cache import LatentCacheView, LatentPagedCache, LatentPagedPool
@@ -195,11 +195,12 @@ class VoluzenModel:
             for layer in self.layers:
                 h = layer.norm1(layer.mixer(h, plan, slabs[layer.slab_index]), residual=x32)
                 if layer.mlp is not None:
-                    h = layer.norm2(layer.mlp(h), residual=x32)
+                    y = layer.mlp(h, wide=True) if isinstance(layer.mlp, GatedMLP) else layer.mlp(h)
+                    h = layer.norm2(y, residual=x32)
             if plan.num_want == 0:  # a portion whose logits nobody asked for: the caches are filled, that is all
                 return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
             rows = x32.index_select(0, plan.want_rows.long())
-            return _linear_f32(self.final_norm(rows), self.head)
+            return linear_wide(self.final_norm(rows), self.head)
         finally:
             if exact:
                 torch.backends.cuda.matmul.allow_tf32 = tf32
@@ -250,22 +251,3 @@ class VoluzenModel:
         out = torch.zeros((B, keep, self.vocab_size), dtype=logits.dtype, device=logits.device)
         out[torch.tensor(live, device=logits.device)] = logits
         return out
-
-
-_F32_OUT = {"ok": None}
-
-
-def _linear_f32(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """``h @ w.T`` with the fp32 accumulator handed back unrounded (logits), where the library product can do that for
-    these shapes; else the product in the compute dtype, widened."""
-    if h.dtype == torch.float32:
-        return linear(h, w)
-    if _F32_OUT["ok"] is not False:
-        try:
-            out = torch.mm(h, w.t(), out_dtype=torch.float32)
-            _F32_OUT["ok"] = True
-            return out
-        except (TypeError, RuntimeError):
-            if _F32_OUT["ok"] is None:
-                _F32_OUT["ok"] = False  # this torch has no such product at all
-    return linear(h, w).float()
