@@ -155,7 +155,7 @@ def run_attention(dev, dtype, q_full, rows, positions, rank, window, scale, page
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("rank,rot,heads", [(32, 8, 2), (96, 16, 4), (130, 6, 5), (33, 6, 3), (512, 64, 3)])
+@pytest.mark.parametrize("rank,rot,heads", [(32, 8, 2), (96, 16, 4), (130, 6, 5), (33, 6, 3), (512, 64, 3), (640, 32, 2)])
 def test_latent_attention_against_plain_attention(dev, dtype, rank, rot, heads):
     g = torch.Generator().manual_seed(rank)
     S = 150

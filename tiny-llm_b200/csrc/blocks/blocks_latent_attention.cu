@@ -134,7 +134,7 @@ static int launch(const void *q_lat, long long ql_token, long long ql_head, cons
     size_t smem = ((size_t)kRows * width + (size_t)kKeys * (width + 1)) * sizeof(float);
     auto kernel = latent_attention_kernel<T, RL>;
     if (smem > 48 * 1024) {
-        if (smem > 200 * 1024) return tl::fail(TL_EINVAL, "latent_attention: rank + rot = %d does not fit in shared memory", width);
+        if (smem > 227 * 1024) return tl::fail(TL_EINVAL, "latent_attention: rank + rot = %d does not fit in shared memory", width);
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return tl::fail(TL_ECUDA, "latent_attention: %s", cudaGetErrorString(e));
     }
@@ -158,14 +158,14 @@ extern "C" int tlb_latent_attention(const void *q_lat, long long ql_token, long 
         max_pages <= 0 || num_pages <= 0)
         return tl::fail(TL_EINVAL, "latent_attention: bad argument");
     if (page_size <= 0 || page_size % kKeys != 0) return tl::fail(TL_EINVAL, "latent_attention: page_size must be a multiple of %d", kKeys);
-    if (rank > 512) return tl::fail(TL_EINVAL, "latent_attention: rank %d > 512", rank);
+    if (rank > 1024) return tl::fail(TL_EINVAL, "latent_attention: rank %d > 1024", rank);
     cudaStream_t st = as_stream(stream);
     int rl = ceil_div(rank, 32);
     int rc = TL_OK;
 #define TLB_LA(RLV)                                                                                                                          \
     rc = launch<T, RLV>(q_lat, ql_token, ql_head, q_rot ? q_rot : q_lat, qr_token, qr_head, slab, num_pages, page_size, rank, rot, block_table, \
                         max_pages, tiles, num_tiles, tok_pos, heads, window, scale, out, o_token, o_head, st)
-    TLB_DISPATCH(dtype, "latent_attention", if (rl <= 4) TLB_LA(4); else if (rl <= 8) TLB_LA(8); else TLB_LA(16));
+    TLB_DISPATCH(dtype, "latent_attention", if (rl <= 4) TLB_LA(4); else if (rl <= 8) TLB_LA(8); else if (rl <= 16) TLB_LA(16); else TLB_LA(32));
 #undef TLB_LA
     if (rc != TL_OK) return rc;
     TL_LAUNCH_CHECK("latent_attention");
