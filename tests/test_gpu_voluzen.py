@@ -165,7 +165,7 @@ def test_latent_attention_against_plain_attention(dev, dtype, rank, rot, heads):
     for window in (0, 1, 33, 40):
         want = O.cache_attention(q.double(), rows.double(), positions, rank, window, 0.11)
         got = run_attention(dev, dtype, q, rows, positions, rank, window, 0.11)
-        close(got, want, 2e-6 if dtype == torch.float32 else 1.5e-2)
+        close(got, want, 5e-6 if dtype == torch.float32 else 1.5e-2)  # fp32: scores are dot products of up to 672 terms
 
 
 @pytest.mark.parametrize("rank,rot,heads", [(32, 8, 1), (96, 16, 4), (130, 6, 5), (64, 32, 16), (256, 64, 40), (64, 8, 70), (512, 64, 3)])

@@ -203,10 +203,8 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
         {
             int g = lane >> 2;
             float a_lo = s_alpha[mt * 16 + g], a_hi = s_alpha[mt * 16 + g + 8];
-            if (a_lo != 1.f || a_hi != 1.f) {  // once the running maxima have settled nothing needs rescaling
 #pragma unroll
-                for (int i = 0; i < 2 * PAIRS; ++i) acc[i][0] *= a_lo, acc[i][1] *= a_lo, acc[i][2] *= a_hi, acc[i][3] *= a_hi;
-            }
+            for (int i = 0; i < 2 * PAIRS; ++i) acc[i][0] *= a_lo, acc[i][1] *= a_lo, acc[i][2] *= a_hi, acc[i][3] *= a_hi;
 #pragma unroll
             for (int kk = 0; kk < kMKeys / 16; ++kk) {
                 uint32_t a0, a1, a2, a3;
