@@ -75,7 +75,7 @@ int tlb_latent_attention(const void *q_lat, long long ql_token, long long ql_hea
 
 /* The same on the tensor cores, for the bf16 cache: 32 query rows per CTA = tile_tokens consecutive tokens x min(heads, 32)
  * heads, with tile_tokens = tlb_latent_attention_mma_tile_tokens(heads) the most tokens a tile may hold.  Needs
- * rank <= 512, (rank + rot) % 8 == 0, page_size % 64 == 0 (tlb_latent_attention_mma_supported). */
+ * rank <= 512, (rank + rot) % 8 == 0, page_size % 32 == 0 (tlb_latent_attention_mma_supported). */
 int tlb_latent_attention_mma_tile_tokens(int heads);
 int tlb_latent_attention_mma_supported(int rank, int rot, int page_size);
 int tlb_latent_attention_mma(const void *q_lat, long long ql_token, long long ql_head, const void *q_rot, long long qr_token,

@@ -2,20 +2,21 @@
 //
 // All heads of a token attend the same keys (cache row j = [latent | rotated shared key part]) and mix the same values
 // (the latent part of the row), so a CTA takes 32 query rows = a run of consecutive tokens of one sequence x a group of
-// heads and streams every 64-key tile of the paged cache through shared memory ONCE for all of them (cp.async into a
-// second buffer while the current one is used).  Per key tile, with 8 warps:
-//   1. scores:  the 32 x 64 block S = Q K^T is 2 x 8 blocks of 16 x 8, two per warp (one A fragment feeds both; two
-//               accumulator sets alternate over the reduction so that consecutive MMAs do not wait on each other);
-//   2. softmax: each warp owns 4 rows, 8 lanes per row: mask, running maximum / sum, P = exp(S - m) as bf16, rescale factor;
+// heads and streams every 32-key tile of the paged cache through shared memory ONCE for all of them (cp.async into one
+// buffer: at the widest cache row, 576 entries, a CTA holds 82 KB, so two CTAs share an SM and one computes while the
+// other loads).  Per key tile, with 8 warps:
+//   1. scores:  the 32 x 32 block S = Q K^T is 2 x 4 blocks of 16 x 8, one per warp (two accumulator sets alternate
+//               over the reduction so that consecutive MMAs do not wait on each other);
+//   2. softmax: each warp owns 4 rows, 8 lanes per row, 4 keys per lane: mask, running maximum / sum, P = exp(S - m) as bf16, rescale factor;
 //   3. values:  O[32 x rank] += P V, warp = (16-row half, quarter of the value columns); V is the key tile itself.
-// A row's arithmetic depends only on its own position (64-aligned key tiles in ascending order): what else is in the
+// A row's arithmetic depends only on its own position (32-aligned key tiles in ascending order): what else is in the
 // CTA, the launch or the batch does not change its result.
 #include "blocks_common.cuh"
 
 namespace tlb {
 
 constexpr int kMRows = 32;   // query rows per CTA
-constexpr int kMKeys = 64;   // keys per tile
+constexpr int kMKeys = 32;   // keys per tile
 constexpr int kSS = kMKeys + 1;  // score row stride (floats)
 constexpr int kSP = kMKeys + 8;  // probability row stride (bf16): (stride / 8) odd
 constexpr int kMWarps = 8;
@@ -57,8 +58,8 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int width = rank + rot;
     bf16 *sq = reinterpret_cast<bf16 *>(smem_raw);                  // [32][row_stride]
-    bf16 *sk0 = sq + kMRows * row_stride;                           // 2 x [32][row_stride]
-    bf16 *sp = sk0 + 2 * kMKeys * row_stride;                       // [32][kSP]
+    bf16 *sk0 = sq + kMRows * row_stride;                           // [32][row_stride], one buffer: two CTAs share an SM and cover each other's loads
+    bf16 *sp = sk0 + kMKeys * row_stride;                       // [32][kSP]
     float *ss = reinterpret_cast<float *>(sp + kMRows * kSP);       // [32][kSS]
     float *s_alpha = ss + kMRows * kSS;                             // [32]
     float *s_l = s_alpha + kMRows;                                  // [32]
@@ -71,7 +72,7 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
     const int chunks = width / 8;  // 16-byte pieces of a cache row
 
     // zero everything once: padding columns of Q and K must read as zero in every product
-    for (int i = threadIdx.x; i < ((kMRows + 2 * kMKeys) * row_stride) / 8; i += blockDim.x) reinterpret_cast<uint4 *>(sq)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < ((kMRows + kMKeys) * row_stride) / 8; i += blockDim.x) reinterpret_cast<uint4 *>(sq)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
     // queries: row = token-in-tile * head_group + head-in-group
     for (int r = warp; r < kMRows; r += kMWarps) {
@@ -123,58 +124,51 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
     // with the key range split over gridDim.z CTAs, this one takes a contiguous run of key tiles
     const int per_split = (n_tiles + (int)gridDim.z - 1) / (int)gridDim.z;
     const int tile_begin = (int)blockIdx.z * per_split, tile_end = min(n_tiles, tile_begin + per_split);
-    if (tile_begin < tile_end) stage(tile_begin, sk0 + (tile_begin & 1) * kMKeys * row_stride);
     const int ksteps = (width + 15) / 16;
-    __syncthreads();  // the queries are staged (also when this split has no tile)
     for (int tile = tile_begin; tile < tile_end; ++tile) {
-        bf16 *sk = sk0 + (tile & 1) * kMKeys * row_stride;
+        bf16 *sk = sk0;
+        __syncthreads();  // every warp is done with the previous tile (and, first time, the zero fill and the queries are in place)
+        stage(tile, sk);
         cp_async_wait<0>();
-        __syncthreads();  // this tile is in shared memory; every warp is done with the previous tile
-        if (tile + 1 < tile_end) stage(tile + 1, sk0 + ((tile + 1) & 1) * kMKeys * row_stride);  // lands while this tile is computed
+        __syncthreads();  // this tile is in shared memory
 
-        // 1. scores: this warp's row half x key blocks nt and nt + 4
+        // 1. scores: this warp's 16 rows x 8 keys, two reduction steps per pair of loads
         {
-            float ca0[4] = {}, ca1[4] = {}, cb0[4] = {}, cb1[4] = {};
+            float ca0[4] = {}, ca1[4] = {};
             const bf16 *qa = sq + (mt * 16 + (lane & 15)) * row_stride + (lane >> 4) * 8;
-            const bf16 *kb = sk + ((nt + ((lane >> 4) & 1) * 4) * 8 + (lane & 7)) * row_stride + ((lane >> 3) & 1) * 8;
+            const bf16 *kb = sk + (nt * 8 + (lane & 7)) * row_stride + (lane >> 3) * 8;  // 4 matrices = 32 reduction columns of 8 keys
             int ks = 0;
             for (; ks + 1 < ksteps; ks += 2) {
-                uint32_t a0, a1, a2, a3, b0, b1, b2, b3, e0, e1, e2, e3, f0, f1, f2, f3;
+                uint32_t a0, a1, a2, a3, e0, e1, e2, e3, b0, b1, b2, b3;
                 ldmatrix_x4(a0, a1, a2, a3, qa + ks * 16);
-                ldmatrix_x4(b0, b1, b2, b3, kb + ks * 16);
                 ldmatrix_x4(e0, e1, e2, e3, qa + ks * 16 + 16);
-                ldmatrix_x4(f0, f1, f2, f3, kb + ks * 16 + 16);
+                ldmatrix_x4(b0, b1, b2, b3, kb + ks * 16);
                 mma_bf16(ca0, a0, a1, a2, a3, b0, b1);
-                mma_bf16(cb0, a0, a1, a2, a3, b2, b3);
-                mma_bf16(ca1, e0, e1, e2, e3, f0, f1);
-                mma_bf16(cb1, e0, e1, e2, e3, f2, f3);
+                mma_bf16(ca1, e0, e1, e2, e3, b2, b3);
             }
             if (ks < ksteps) {
-                uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                uint32_t a0, a1, a2, a3, b0, b1;
                 ldmatrix_x4(a0, a1, a2, a3, qa + ks * 16);
-                ldmatrix_x4(b0, b1, b2, b3, kb + ks * 16);
+                ldmatrix_x2(b0, b1, kb + ks * 16);
                 mma_bf16(ca0, a0, a1, a2, a3, b0, b1);
-                mma_bf16(cb0, a0, a1, a2, a3, b2, b3);
             }
             int g = lane >> 2, t = lane & 3;
             float *o = ss + (mt * 16 + g) * kSS + nt * 8 + 2 * t;
             o[0] = (ca0[0] + ca1[0]) * scale, o[1] = (ca0[1] + ca1[1]) * scale;
             o[8 * kSS] = (ca0[2] + ca1[2]) * scale, o[8 * kSS + 1] = (ca0[3] + ca1[3]) * scale;
-            o[32] = (cb0[0] + cb1[0]) * scale, o[33] = (cb0[1] + cb1[1]) * scale;
-            o[8 * kSS + 32] = (cb0[2] + cb1[2]) * scale, o[8 * kSS + 33] = (cb0[3] + cb1[3]) * scale;
         }
         __syncthreads();
 
-        // 2. softmax over this tile's keys: a warp owns 4 rows, 8 lanes per row, 8 keys per lane (keys lq + 8 j)
+        // 2. softmax over this tile's keys: a warp owns 4 rows, 8 lanes per row, 4 keys per lane (keys lq + 8 j)
         {
             const int i = lane >> 3, lq = lane & 7, r = warp * 4 + i;
             const int key0 = lo + tile * kMKeys + lq;
             const int rp = pos_row;
             const bool live = live_row;
-            float sv[8];
+            float sv[kMKeys / 8];
             float mx = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < kMKeys / 8; ++j) {
                 int key = key0 + 8 * j;
                 bool vis = live && key <= rp && (window <= 0 || rp - key < window);
                 sv[j] = vis ? ss[r * kSS + lq + 8 * j] : -INFINITY;
@@ -186,7 +180,7 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
             float alpha = m_new == -INFINITY ? 1.f : expf(m_row - m_new);
             float sum = 0.f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < kMKeys / 8; ++j) {
                 bf16 pb = __float2bfloat16_rn(sv[j] == -INFINITY ? 0.f : expf(sv[j] - m_new));
                 sum += __bfloat162float(pb);  // the rounded probability: numerator and denominator see the same weights
                 sp[r * kSP + lq + 8 * j] = pb;
@@ -326,7 +320,7 @@ extern "C" int tlb_latent_attention_mma(const void *q_lat, long long ql_token, l
     if (!q_lat || (!q_rot && rot > 0) || !slab || !block_table || !tiles || !tok_pos || !out || heads <= 0 || max_pages <= 0 || num_pages <= 0)
         return tl::fail(TL_EINVAL, "latent_attention_mma: bad argument");
     if (!tlb_latent_attention_mma_supported(rank, rot, page_size))
-        return tl::fail(TL_EINVAL, "latent_attention_mma: rank <= 512, (rank + rot) %% 8 == 0 and page_size %% 64 == 0 are required");
+        return tl::fail(TL_EINVAL, "latent_attention_mma: rank <= 512, (rank + rot) %% 8 == 0 and page_size %% 32 == 0 are required");
     if (!tl::aligned16(slab)) return tl::fail(TL_EINVAL, "latent_attention_mma: the cache must be 16-byte aligned");
     int width = rank + rot;
     int pairs = mma_pairs(rank);
@@ -337,7 +331,7 @@ extern "C" int tlb_latent_attention_mma(const void *q_lat, long long ql_token, l
     float *part = splits > 1 ? (float *)workspace : nullptr;
     int span = max(ceil_div(width, 16) * 16, 64 * pairs);  // columns a row must hold: the padded key width, the four value quarters
     int row_stride = span + 8;                              // (stride / 8) odd: conflict-free ldmatrix rows
-    size_t smem = (size_t)(kMRows + 2 * kMKeys) * row_stride * 2 + kMRows * kSP * 2 + (size_t)kMRows * kSS * 4 + 2 * kMRows * 4;
+    size_t smem = (size_t)(kMRows + kMKeys) * row_stride * 2 + kMRows * kSP * 2 + (size_t)kMRows * kSS * 4 + 2 * kMRows * 4;
     int head_group = heads >= kMRows ? kMRows : heads;
     dim3 grid(num_tiles, ceil_div(heads, head_group), splits);
     cudaStream_t st = as_stream(stream);
