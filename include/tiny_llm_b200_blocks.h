@@ -41,6 +41,14 @@ int tlb_embed_rows(const int32_t *ids, const void *table, float *x32, void *h, i
 int tlb_norm_residual(const void *y, int y_is_f32, const void *w, float weight_offset, const void *scale, float eps, float *residual,
                       void *h, int rows, int dim, int dtype, void *stream);
 
+/* End of a layer whose sublayers read one norm of the stream, fused with the next norm: residual += a (+ b, if b != NULL)
+ * in fp32, then, if w != NULL, h = residual / rms(residual) * w rounded to `dtype`. */
+int tlb_add_norm(float *residual, const float *a, const float *b, const void *w, float eps, void *h, int rows, int dim, int dtype, void *stream);
+
+/* y = coef * (a / rms(a) * wa + b / rms(b) * wb); a, b, y fp32 [rows, dim], wa, wb `dtype` [dim]. */
+int tlb_norm_mix2(const float *a, const void *wa, const float *b, const void *wb, float coef, float eps, float *y, int rows, int dim, int dtype,
+                  void *stream);
+
 /* Rotary positions, in place, on `dims` entries starting at `first` within every head of x [rows, heads] (strides in
  * elements).  interleaved = 0: pair (i, i + dims/2); 1: pair (2i, 2i+1).  angle = tok_pos[row] * base^(-2i/dims). */
 int tlb_rope_rows(void *x, long long row_stride, long long head_stride, int first, int heads, int dims, int interleaved, double base,
@@ -87,13 +95,47 @@ int tlb_latent_attention_mma(const void *q_lat, long long ql_token, long long ql
  * launch merges the partial sums; workspace: tlb_latent_attention_mma_workspace(...) bytes, no initialisation needed. */
 size_t tlb_latent_attention_mma_workspace(int num_tiles, int heads, int rank, int splits);
 
+/* Grouped-query softmax attention over a paged cache whose row (one token) is [kv_heads * dk keys | kv_heads * dv values].
+ * q [T, heads, dk] and out [T, heads, dv] are views with token / head strides in elements.  Token t sees key j <= tok_pos[t]
+ * and, mask 1: tok_pos[t] - j < mask_size (sliding window); mask 2: j / mask_size == tok_pos[t] / mask_size (chunks counted
+ * from position 0); mask 0: all.  score = scale * q.k, then softcap * tanh(score / softcap) when softcap > 0; sink != 0 adds
+ * exp(0) to the softmax's denominator; gate != NULL multiplies head h's output by sigmoid(gate[t * g_token + h]).
+ * tiles [num_tiles, 3] as for latent attention, cut to at most tlb_paged_attention_tile_tokens(heads, kv_heads) tokens. */
+int tlb_paged_attention_tile_tokens(int heads, int kv_heads);
+int tlb_paged_attention(const void *q, long long q_token, long long q_head, const void *slab, int num_pages, int page_size, int dk, int dv,
+                        int heads, int kv_heads, const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles,
+                        const int32_t *tok_pos, int mask, int mask_size, float scale, float softcap, int sink, const void *gate,
+                        long long g_token, void *out, long long o_token, long long o_head, int dtype, void *stream);
+/* Before that attention: per-head RMS norm (plain weight [dk]) of the queries in place (q_norm != NULL) and of the keys
+ * (k_norm != NULL), and the token's keys and values stored at its slot of the cache (k != NULL). */
+int tlb_kv_prepare(void *q, long long q_token, long long q_head, int heads, const void *q_norm, const void *k, long long k_token, long long k_head,
+                   const void *v, long long v_token, long long v_head, int kv_heads, int dk, int dv, const void *k_norm, float eps,
+                   const int32_t *tok_pos, const int32_t *tok_seq, const int32_t *block_table, int max_pages, int num_pages, int page_size,
+                   void *slab, int tokens, int dtype, void *stream);
+
+/* Linear attention with a per-channel decay, state in fp32 slots.  Per sequence and head S [dk, dv]:
+ *   alpha = sigmoid(z + z_bias)^(1 / tau);  S <- diag(alpha) S + k v^T;  out = S^T (q_scale * q)
+ * seq_info [num_seqs, 4] int32: first flat token, token count, position of the first token, state slot.  A sequence at
+ * position 0 starts from zero; the slot (state + slot * slot_stride floats, [heads, dk, dv]) is written after the last
+ * token.  q, k [T, heads, dk], v [T, heads, dv] views (strides in elements), z [T, heads * dk] fp32 rows z_token apart,
+ * z_bias `dtype` or NULL, out [T, heads, dv] fp32 contiguous.  dk <= 128. */
+int tlb_decay_scan(const void *q, long long q_token, long long q_head, const void *k, long long k_token, long long k_head, const void *v,
+                   long long v_token, long long v_head, const float *z, long long z_token, const void *z_bias, float tau, float q_scale, int heads,
+                   int dk, int dv, const int32_t *seq_info, int num_seqs, float *state, long long slot_stride, int num_slots, float *out, int dtype,
+                   void *stream);
+/* out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w * act(gate[t, h, :]) (gate rows g_token apart, NULL = no gate; act 0 = the gate
+ * as it is, 1 = silu); o fp32 [tokens, heads, dv], out `dtype` [tokens, heads * dv]. */
+int tlb_head_norm_gate(const float *o, const void *w, float eps, const void *gate, long long g_token, int act, void *out, int tokens, int heads,
+                       int dv, int dtype, void *stream);
+
 /* out[t, j] = act(gu[t, j]) * gu[t, width + j]; act 0 = silu, 1 = gelu (tanh form). */
 int tlb_gated_act(const void *gu, void *out, int rows, int width, int act, int dtype, void *stream);
 
-/* Router: logits = W h + b in fp32 (h, W, b stored in `dtype`), the `top` largest per token (lower index wins a tie),
- * weights = softmax over the chosen logits.  idx [tokens, top] int32, gate [tokens, top] fp32. */
-int tlb_moe_route(const void *h, const void *w, const void *b, int tokens, int dim, int experts, int top, int32_t *idx, float *gate,
-                  int dtype, void *stream);
+/* Router: logits = W h + b in fp32 (h, W, b stored in `dtype`; b may be NULL), the `top` largest per token (lower index
+ * wins a tie).  scoring 0: weights = softmax over the chosen logits; 1: weights = sigmoid of each chosen logit, not
+ * renormalised.  idx [tokens, top] int32, gate [tokens, top] fp32. */
+int tlb_moe_route(const void *h, const void *w, const void *b, int tokens, int dim, int experts, int top, int scoring, int32_t *idx,
+                  float *gate, int dtype, void *stream);
 
 /* Rows per expert tile of the grouped products: 32, or 64 for the tensor-core kernels (bf16, reduction length % 8 == 0)
  * when experts get many rows (half the weight traffic per row). */
@@ -108,10 +150,17 @@ int tlb_moe_sort(const int32_t *idx, int tokens, int top, int experts, int tile_
 int tlb_moe_gate_up(const void *h, const void *wg, const void *wu, const int32_t *sorted_pair, const int32_t *tile_expert,
                     const int32_t *counters, int tokens, int top, int experts, int tile_rows, int dim, int ff, int act, void *inter,
                     int dtype, void *stream);
+/* Experts without a gate: inter[row, :] = act(Wu[e] a[src(row)]) with a = h (token rows, rows_are_pairs = 0) or one row per
+ * (token, choice) pair (rows_are_pairs = 1).  act 0 = silu, 1 = gelu (tanh form), 2 = squared relu. */
+int tlb_moe_up(const void *a, const void *wu, const int32_t *sorted_pair, const int32_t *tile_expert, const int32_t *counters, int tokens,
+               int top, int experts, int tile_rows, int dim, int ff, int act, int rows_are_pairs, void *inter, int dtype, void *stream);
+/* out[t * top + k, :] = gate[t, k] * h[t, :] rounded to `dtype`: inputs of experts whose weight multiplies the input. */
+int tlb_moe_scale_rows(const void *h, const float *gate, void *out, int tokens, int top, int dim, int dtype, void *stream);
 /* pair_out[pair, :] = Wd[e] inter[row, :] (fp32); Wd [experts, dim, ff]. */
 int tlb_moe_down(const void *inter, const void *wd, const int32_t *sorted_pair, const int32_t *tile_expert, const int32_t *counters,
                  int tokens, int top, int experts, int tile_rows, int dim, int ff, float *pair_out, int dtype, void *stream);
-/* y[t,:] = sum_k gate[t,k] * pair_out[t*top+k,:] (+ shared[t,:] if shared != NULL, stored in `dtype`), fp32, in choice order. */
+/* y[t,:] = sum_k gate[t,k] * pair_out[t*top+k,:] (+ shared[t,:] if shared != NULL, stored in `dtype`), fp32, in choice order;
+ * gate == NULL: every weight is 1. */
 int tlb_moe_combine(const float *pair_out, const float *gate, const void *shared, float *y, int tokens, int top, int dim, int dtype,
                     void *stream);
 

@@ -13,15 +13,23 @@ constexpr int kTileRows = TLB_MOE_TILE_ROWS;
 
 __device__ __forceinline__ float moe_act(float z, int act) {
     if (act == 0) return z / (1.0f + expf(-z));
+    if (act == 2) return z > 0.f ? z * z : 0.f;  // squared ReLU
     float inner = 0.7978845608028654f * (z + 0.044715f * z * z * z);
     return 0.5f * z * (1.0f + tanhf(inner));
+}
+
+// Which rows of `a` a tile's rows read: the sorted rows themselves (the second product), the token of the pair, or the pair.
+constexpr int kGatherSorted = 0, kGatherToken = 1, kGatherPair = 2;
+__device__ __forceinline__ int moe_src_row(int pair, int sorted_row, int top, int gather) {
+    if (pair < 0) return -1;
+    return gather == kGatherSorted ? sorted_row : gather == kGatherToken ? pair / top : pair;
 }
 
 // One CTA per token: the row of h is staged in shared memory as fp32, the warps share the experts (each logit is one
 // warp's dot product in a fixed lane order, so it does not depend on the launch), then warp 0 picks the top-k.
 template <typename T>
 __global__ void __launch_bounds__(256)
-moe_route_kernel(const T *__restrict__ h, const T *__restrict__ w, const T *__restrict__ b, int tokens, int dim, int experts, int top,
+moe_route_kernel(const T *__restrict__ h, const T *__restrict__ w, const T *__restrict__ b, int tokens, int dim, int experts, int top, int scoring,
                  int32_t *__restrict__ idx, float *__restrict__ gate) {
     extern __shared__ float route_smem[];
     float *x = route_smem;        // [dim]
@@ -54,7 +62,8 @@ moe_route_kernel(const T *__restrict__ h, const T *__restrict__ w, const T *__re
             if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
         }
         if (k == 0) first_v = bv;
-        float p = expf(bv - first_v);  // the first choice is the largest logit
+        // scoring 0: softmax over the chosen logits (the first choice is the largest); 1: each choice's own sigmoid, as it is
+        float p = scoring == 1 ? 1.0f / (1.0f + expf(-bv)) : expf(bv - first_v);
         denom += p;
         if (lane == 0) {
             idx[(size_t)t * top + k] = bi;
@@ -63,6 +72,7 @@ moe_route_kernel(const T *__restrict__ h, const T *__restrict__ w, const T *__re
         }
         __syncwarp();
     }
+    if (scoring == 1) return;
     for (int k = lane; k < top; k += 32) gate[(size_t)t * top + k] /= denom;
 }
 
@@ -104,7 +114,7 @@ constexpr int kBN = 64, kBK = 16;
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_grouped_kernel(const T *__restrict__ a, const T *__restrict__ w1, const T *__restrict__ w2, const int32_t *__restrict__ sorted_pair,
-                   const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ counters, int top, int K, int N, int act,
+                   const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ counters, int top, int K, int N, int act, int gather,
                    T *__restrict__ inter, float *__restrict__ pair_out) {
     if ((int)blockIdx.x >= counters[0]) return;
     __shared__ float sa[kBK][kTileRows + 1];
@@ -114,9 +124,8 @@ moe_grouped_kernel(const T *__restrict__ a, const T *__restrict__ w1, const T *_
     const int e = tile_expert[blockIdx.x];
     const int row0 = blockIdx.x * kTileRows, col0 = blockIdx.y * kBN;
     if (threadIdx.x < kTileRows) {
-        int pair = sorted_pair[row0 + threadIdx.x];
-        // gate/up gather token rows of h; the down product reads the sorted intermediate rows
-        src_row[threadIdx.x] = pair < 0 ? -1 : (GATED ? pair / top : row0 + (int)threadIdx.x);
+        // the first product gathers rows of h (or of its scaled copy); the second reads the sorted intermediate rows
+        src_row[threadIdx.x] = moe_src_row(sorted_pair[row0 + threadIdx.x], row0 + (int)threadIdx.x, top, gather);
     }
     __syncthreads();
     const T *wa = w1 + (size_t)e * N * K;
@@ -163,6 +172,7 @@ moe_grouped_kernel(const T *__restrict__ a, const T *__restrict__ w1, const T *_
             int col = col0 + tx + 16 * c;
             if (col >= N) continue;
             if (GATED) inter[(size_t)row * N + col] = from_f<T>(moe_act(c1[r][c], act) * c2[r][c]);
+            else if (inter) inter[(size_t)row * N + col] = from_f<T>(moe_act(c1[r][c], act));
             else pair_out[(size_t)pair * N + col] = c1[r][c];
         }
     }
@@ -193,7 +203,7 @@ __device__ __forceinline__ void moe_cp16(void *dst, const void *src, bool ok) {
 template <bool GATED, int BM>
 __global__ void __launch_bounds__(256)
 moe_grouped_mma_kernel(const bf16 *__restrict__ a, const bf16 *__restrict__ w1, const bf16 *__restrict__ w2, const int32_t *__restrict__ sorted_pair,
-                       const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ counters, int top, int K, int N, int act,
+                       const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ counters, int top, int K, int N, int act, int gather,
                        bf16 *__restrict__ inter, float *__restrict__ pair_out) {
     if ((int)blockIdx.x >= counters[0]) return;
     constexpr int MT = BM / 16;          // 16-row halves/quarters of the tile
@@ -207,8 +217,7 @@ moe_grouped_mma_kernel(const bf16 *__restrict__ a, const bf16 *__restrict__ w1, 
     const int e = tile_expert[blockIdx.x];
     const int row0 = blockIdx.x * BM, col0 = blockIdx.y * kTN;
     if (threadIdx.x < BM) {
-        int pair = sorted_pair[row0 + threadIdx.x];
-        src_row[threadIdx.x] = pair < 0 ? -1 : (GATED ? pair / top : row0 + (int)threadIdx.x);
+        src_row[threadIdx.x] = moe_src_row(sorted_pair[row0 + threadIdx.x], row0 + (int)threadIdx.x, top, gather);
     }
     __syncthreads();
     const bf16 *wa = w1 + (size_t)e * N * K;
@@ -277,10 +286,20 @@ moe_grouped_mma_kernel(const bf16 *__restrict__ a, const bf16 *__restrict__ w1, 
                 if (col >= N) continue;
                 float v = c1[i][half * 2 + j];
                 if (GATED) inter[(size_t)row * N + col] = __float2bfloat16_rn(moe_act(v, act) * c2[i][half * 2 + j]);
+                else if (inter) inter[(size_t)row * N + col] = __float2bfloat16_rn(moe_act(v, act));
                 else pair_out[(size_t)pair * N + col] = v;
             }
         }
     }
+}
+
+// out[pair, :] = gate[pair] * h[pair / top, :] rounded to T: the rows of experts whose weight multiplies their input.
+template <typename T>
+__global__ void moe_scale_rows_kernel(const T *__restrict__ h, const float *__restrict__ gate, T *__restrict__ out, int top, int dim) {
+    const int pair = blockIdx.x;
+    const float g = gate[pair];
+    const T *src = h + (size_t)(pair / top) * dim;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) out[(size_t)pair * dim + d] = from_f<T>(g * to_f(src[d]));
 }
 
 template <typename T>
@@ -289,7 +308,7 @@ __global__ void moe_combine_kernel(const float *__restrict__ pair_out, const flo
     int t = blockIdx.x;
     for (int d = threadIdx.x; d < dim; d += blockDim.x) {
         float s = 0.f;
-        for (int k = 0; k < top; ++k) s = fmaf(gate[(size_t)t * top + k], pair_out[((size_t)t * top + k) * dim + d], s);
+        for (int k = 0; k < top; ++k) s = fmaf(gate ? gate[(size_t)t * top + k] : 1.f, pair_out[((size_t)t * top + k) * dim + d], s);
         if (shared) s += to_f(shared[(size_t)t * dim + d]);
         y[(size_t)t * dim + d] = s;
     }
@@ -301,14 +320,15 @@ using namespace tlb;
 
 template <bool GATED, int BM>
 static int launch_grouped_mma(dim3 grid, cudaStream_t st, const bf16 *a, const bf16 *w1, const bf16 *w2, const int32_t *sorted_pair,
-                              const int32_t *tile_expert, const int32_t *counters, int top, int K, int N, int act, bf16 *inter, float *pair_out) {
+                              const int32_t *tile_expert, const int32_t *counters, int top, int K, int N, int act, int gather, bf16 *inter,
+                              float *pair_out) {
     size_t smem = (size_t)2 * (BM + kTN * (GATED ? 2 : 1)) * kTS * sizeof(bf16);
     auto kernel = moe_grouped_mma_kernel<GATED, BM>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return tl::fail(TL_ECUDA, "moe_grouped: %s", cudaGetErrorString(e));
     }
-    kernel<<<grid, 256, smem, st>>>(a, w1, w2, sorted_pair, tile_expert, counters, top, K, N, act, inter, pair_out);
+    kernel<<<grid, 256, smem, st>>>(a, w1, w2, sorted_pair, tile_expert, counters, top, K, N, act, gather, inter, pair_out);
     return TL_OK;
 }
 
@@ -318,15 +338,16 @@ static bool moe_mma_ok(int dtype, int k, const void *a, const void *w1, const vo
 
 extern "C" {
 
-int tlb_moe_route(const void *h, const void *w, const void *b, int tokens, int dim, int experts, int top, int32_t *idx, float *gate, int dtype,
-                  void *stream) {
+int tlb_moe_route(const void *h, const void *w, const void *b, int tokens, int dim, int experts, int top, int scoring, int32_t *idx, float *gate,
+                  int dtype, void *stream) {
     if (tokens <= 0) return TL_OK;
-    if (!h || !w || !idx || !gate || dim <= 0 || experts <= 0 || top <= 0 || top > experts) return tl::fail(TL_EINVAL, "moe_route: bad argument");
+    if (!h || !w || !idx || !gate || dim <= 0 || experts <= 0 || top <= 0 || top > experts || scoring < 0 || scoring > 1)
+        return tl::fail(TL_EINVAL, "moe_route: bad argument");
     size_t smem = ((size_t)dim + experts) * sizeof(float);
     if (smem > 48 * 1024) return tl::fail(TL_EINVAL, "moe_route: width %d + %d experts do not fit", dim, experts);
     TLB_DISPATCH(dtype, "moe_route",
-                 moe_route_kernel<T><<<tokens, 256, smem, as_stream(stream)>>>((const T *)h, (const T *)w, (const T *)b, tokens, dim, experts, top, idx,
-                                                                             gate));
+                 moe_route_kernel<T><<<tokens, 256, smem, as_stream(stream)>>>((const T *)h, (const T *)w, (const T *)b, tokens, dim, experts, top, scoring,
+                                                                             idx, gate));
     TL_LAUNCH_CHECK("moe_route");
     return TL_OK;
 }
@@ -361,9 +382,9 @@ int tlb_moe_gate_up(const void *h, const void *wg, const void *wu, const int32_t
     if (moe_mma_ok(dtype, dim, h, wg, wu)) {
         dim3 tc((unsigned)(tlb_moe_max_rows(tokens, top, experts, tile_rows) / tile_rows), ceil_div(ff, kTN));
         int rc = tile_rows == 64 ? launch_grouped_mma<true, 64>(tc, as_stream(stream), (const bf16 *)h, (const bf16 *)wg, (const bf16 *)wu, sorted_pair,
-                                                                tile_expert, counters, top, dim, ff, act, (bf16 *)inter, nullptr)
+                                                                tile_expert, counters, top, dim, ff, act, kGatherToken, (bf16 *)inter, nullptr)
                                  : launch_grouped_mma<true, 32>(tc, as_stream(stream), (const bf16 *)h, (const bf16 *)wg, (const bf16 *)wu, sorted_pair,
-                                                                tile_expert, counters, top, dim, ff, act, (bf16 *)inter, nullptr);
+                                                                tile_expert, counters, top, dim, ff, act, kGatherToken, (bf16 *)inter, nullptr);
         if (rc != TL_OK) return rc;
         TL_LAUNCH_CHECK("moe_gate_up");
         return TL_OK;
@@ -372,8 +393,44 @@ int tlb_moe_gate_up(const void *h, const void *wg, const void *wu, const int32_t
     dim3 grid((unsigned)(tlb_moe_max_rows(tokens, top, experts, kTileRows) / kTileRows), ceil_div(ff, kBN));
     TLB_DISPATCH(dtype, "moe_gate_up",
                  moe_grouped_kernel<T, true><<<grid, 256, 0, as_stream(stream)>>>((const T *)h, (const T *)wg, (const T *)wu, sorted_pair, tile_expert,
-                                                                                 counters, top, dim, ff, act, (T *)inter, nullptr));
+                                                                                 counters, top, dim, ff, act, kGatherToken, (T *)inter, nullptr));
     TL_LAUNCH_CHECK("moe_gate_up");
+    return TL_OK;
+}
+
+// The first product of experts without a gate: inter[row, :] = act(W[e] a[src(row)]), a = token rows (rows_are_pairs = 0) or one row per
+// (token, choice) pair (rows_are_pairs = 1: the scaled copies tlb_moe_scale_rows makes).
+int tlb_moe_up(const void *a, const void *wu, const int32_t *sorted_pair, const int32_t *tile_expert, const int32_t *counters, int tokens, int top,
+               int experts, int tile_rows, int dim, int ff, int act, int rows_are_pairs, void *inter, int dtype, void *stream) {
+    if (tokens <= 0) return TL_OK;
+    if (!a || !wu || !sorted_pair || !tile_expert || !counters || !inter || dim <= 0 || ff <= 0 || top <= 0 || act < 0 || act > 2)
+        return tl::fail(TL_EINVAL, "moe_up: bad argument");
+    int gather = rows_are_pairs ? kGatherPair : kGatherToken;
+    if (moe_mma_ok(dtype, dim, a, wu, nullptr)) {
+        dim3 tc((unsigned)(tlb_moe_max_rows(tokens, top, experts, tile_rows) / tile_rows), ceil_div(ff, kTN));
+        int rc = tile_rows == 64 ? launch_grouped_mma<false, 64>(tc, as_stream(stream), (const bf16 *)a, (const bf16 *)wu, nullptr, sorted_pair, tile_expert,
+                                                                 counters, top, dim, ff, act, gather, (bf16 *)inter, nullptr)
+                                 : launch_grouped_mma<false, 32>(tc, as_stream(stream), (const bf16 *)a, (const bf16 *)wu, nullptr, sorted_pair, tile_expert,
+                                                                 counters, top, dim, ff, act, gather, (bf16 *)inter, nullptr);
+        if (rc != TL_OK) return rc;
+        TL_LAUNCH_CHECK("moe_up");
+        return TL_OK;
+    }
+    if (tile_rows != kTileRows) return tl::fail(TL_EINVAL, "moe_up: %d-row tiles need the tensor-core kernel", tile_rows);
+    dim3 grid((unsigned)(tlb_moe_max_rows(tokens, top, experts, kTileRows) / kTileRows), ceil_div(ff, kBN));
+    TLB_DISPATCH(dtype, "moe_up",
+                 moe_grouped_kernel<T, false><<<grid, 256, 0, as_stream(stream)>>>((const T *)a, (const T *)wu, nullptr, sorted_pair, tile_expert, counters,
+                                                                                  top, dim, ff, act, gather, (T *)inter, nullptr));
+    TL_LAUNCH_CHECK("moe_up");
+    return TL_OK;
+}
+
+int tlb_moe_scale_rows(const void *h, const float *gate, void *out, int tokens, int top, int dim, int dtype, void *stream) {
+    if (tokens <= 0) return TL_OK;
+    if (!h || !gate || !out || top <= 0 || dim <= 0) return tl::fail(TL_EINVAL, "moe_scale_rows: bad argument");
+    TLB_DISPATCH(dtype, "moe_scale_rows",
+                 moe_scale_rows_kernel<T><<<tokens * top, 128, 0, as_stream(stream)>>>((const T *)h, gate, (T *)out, top, dim));
+    TL_LAUNCH_CHECK("moe_scale_rows");
     return TL_OK;
 }
 
@@ -385,9 +442,9 @@ int tlb_moe_down(const void *inter, const void *wd, const int32_t *sorted_pair, 
     if (moe_mma_ok(dtype, ff, inter, wd, nullptr)) {
         dim3 tc((unsigned)(tlb_moe_max_rows(tokens, top, experts, tile_rows) / tile_rows), ceil_div(dim, kTN));
         int rc = tile_rows == 64 ? launch_grouped_mma<false, 64>(tc, as_stream(stream), (const bf16 *)inter, (const bf16 *)wd, nullptr, sorted_pair,
-                                                                 tile_expert, counters, top, ff, dim, 0, nullptr, pair_out)
+                                                                 tile_expert, counters, top, ff, dim, 0, kGatherSorted, nullptr, pair_out)
                                  : launch_grouped_mma<false, 32>(tc, as_stream(stream), (const bf16 *)inter, (const bf16 *)wd, nullptr, sorted_pair,
-                                                                 tile_expert, counters, top, ff, dim, 0, nullptr, pair_out);
+                                                                 tile_expert, counters, top, ff, dim, 0, kGatherSorted, nullptr, pair_out);
         if (rc != TL_OK) return rc;
         TL_LAUNCH_CHECK("moe_down");
         return TL_OK;
@@ -396,14 +453,14 @@ int tlb_moe_down(const void *inter, const void *wd, const int32_t *sorted_pair, 
     dim3 grid((unsigned)(tlb_moe_max_rows(tokens, top, experts, kTileRows) / kTileRows), ceil_div(dim, kBN));
     TLB_DISPATCH(dtype, "moe_down",
                  moe_grouped_kernel<T, false><<<grid, 256, 0, as_stream(stream)>>>((const T *)inter, (const T *)wd, nullptr, sorted_pair, tile_expert,
-                                                                                  counters, top, ff, dim, 0, nullptr, pair_out));
+                                                                                  counters, top, ff, dim, 0, kGatherSorted, nullptr, pair_out));
     TL_LAUNCH_CHECK("moe_down");
     return TL_OK;
 }
 
 int tlb_moe_combine(const float *pair_out, const float *gate, const void *shared, float *y, int tokens, int top, int dim, int dtype, void *stream) {
     if (tokens <= 0) return TL_OK;
-    if (!pair_out || !gate || !y || top <= 0 || dim <= 0) return tl::fail(TL_EINVAL, "moe_combine: bad argument");
+    if (!pair_out || !y || top <= 0 || dim <= 0) return tl::fail(TL_EINVAL, "moe_combine: bad argument");
     TLB_DISPATCH(dtype, "moe_combine",
                  moe_combine_kernel<T><<<tokens, 256, 0, as_stream(stream)>>>(pair_out, gate, (const T *)shared, y, top, dim));
     TL_LAUNCH_CHECK("moe_combine");

@@ -120,6 +120,45 @@ __global__ void norm_residual_kernel(const TY *__restrict__ y, const T *__restri
     }
 }
 
+
+// residual += a (+ b) in fp32, then (w != NULL) h = residual / rms(residual) * w rounded to T: the end of a layer whose
+// sublayers both read one norm of the stream, fused with the next layer's norm.
+template <typename T>
+__global__ void add_norm_kernel(float *__restrict__ residual, const float *__restrict__ a, const float *__restrict__ b, const T *__restrict__ w,
+                                float eps, T *__restrict__ h, int dim) {
+    __shared__ float scratch[33];
+    size_t base = (size_t)blockIdx.x * dim;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float x = residual[base + d] + (b ? a[base + d] + b[base + d] : a[base + d]);
+        residual[base + d] = x;
+        ss += x * x;
+    }
+    if (w == nullptr || h == nullptr) return;
+    ss = block_sum(ss, scratch);
+    float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) h[base + d] = from_f<T>(residual[base + d] * inv * to_f(w[d]));
+}
+
+// y = coef * (a / rms(a) * wa + b / rms(b) * wb), fp32 in and out: two mixers side by side, each normed before they meet.
+template <typename T>
+__global__ void norm_mix2_kernel(const float *__restrict__ a, const T *__restrict__ wa, const float *__restrict__ b, const T *__restrict__ wb,
+                                 float coef, float eps, float *__restrict__ y, int dim) {
+    __shared__ float scratch[33];
+    size_t base = (size_t)blockIdx.x * dim;
+    float sa = 0.f, sb = 0.f;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float u = a[base + d], v = b[base + d];
+        sa += u * u;
+        sb += v * v;
+    }
+    sa = block_sum(sa, scratch);
+    sb = block_sum(sb, scratch);
+    float ia = 1.0f / sqrtf(sa / (float)dim + eps), ib = 1.0f / sqrtf(sb / (float)dim + eps);
+    for (int d = threadIdx.x; d < dim; d += blockDim.x)
+        y[base + d] = coef * (a[base + d] * ia * to_f(wa[d]) + b[base + d] * ib * to_f(wb[d]));
+}
+
 template <typename T>
 __global__ void rope_rows_kernel(T *x, long long row_stride, long long head_stride, int first, int heads, int dims, int interleaved,
                                  double log2_base, const int32_t *__restrict__ tok_pos) {
@@ -239,7 +278,7 @@ using namespace tlb;
 
 extern "C" {
 
-int tlb_abi_version(void) { return 2; }
+int tlb_abi_version(void) { return 3; }
 const char *tlb_last_error(void) { return tl::g_error; }
 long long tlb_launch_count(void) { return tl::g_launches.load(std::memory_order_relaxed); }
 
@@ -267,6 +306,26 @@ int tlb_norm_residual(const void *y, int y_is_f32, const void *w, float weight_o
                  else { if (vec) TLB_NORM(T, true); else TLB_NORM(T, false); });
 #undef TLB_NORM
     TL_LAUNCH_CHECK("norm_residual");
+    return TL_OK;
+}
+
+int tlb_add_norm(float *residual, const float *a, const float *b, const void *w, float eps, void *h, int rows, int dim, int dtype, void *stream) {
+    if (rows <= 0) return TL_OK;
+    if (!residual || !a || dim <= 0 || ((w == nullptr) != (h == nullptr))) return tl::fail(TL_EINVAL, "add_norm: bad argument");
+    int threads = dim >= 2048 ? 256 : 128;
+    TLB_DISPATCH(dtype, "add_norm", add_norm_kernel<T><<<rows, threads, 0, as_stream(stream)>>>(residual, a, b, (const T *)w, eps, (T *)h, dim));
+    TL_LAUNCH_CHECK("add_norm");
+    return TL_OK;
+}
+
+int tlb_norm_mix2(const float *a, const void *wa, const float *b, const void *wb, float coef, float eps, float *y, int rows, int dim, int dtype,
+                  void *stream) {
+    if (rows <= 0) return TL_OK;
+    if (!a || !wa || !b || !wb || !y || dim <= 0) return tl::fail(TL_EINVAL, "norm_mix2: bad argument");
+    int threads = dim >= 2048 ? 256 : 128;
+    TLB_DISPATCH(dtype, "norm_mix2",
+                 norm_mix2_kernel<T><<<rows, threads, 0, as_stream(stream)>>>(a, (const T *)wa, b, (const T *)wb, coef, eps, y, dim));
+    TL_LAUNCH_CHECK("norm_mix2");
     return TL_OK;
 }
 

@@ -46,6 +46,8 @@ BLOCKS_SOURCES = [
     "blocks/blocks_latent_attention.cu",
     "blocks/blocks_latent_attention_mma.cu",
     "blocks/blocks_moe.cu",
+    "blocks/blocks_paged_attention.cu",
+    "blocks/blocks_linear_attention.cu",
 ]
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

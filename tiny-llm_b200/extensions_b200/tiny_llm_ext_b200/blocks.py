@@ -36,7 +36,16 @@ _SIGNATURES = {
                                       ctypes.c_size_t, _VP]),
     "tlb_latent_attention_mma_workspace": (ctypes.c_size_t, [_I, _I, _I, _I]),
     "tlb_gated_act": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
-    "tlb_moe_route": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _VP, _VP, _I, _VP]),
+    "tlb_moe_route": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _VP, _I, _VP]),
+    "tlb_moe_up": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _VP, _I, _VP]),
+    "tlb_moe_scale_rows": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _VP]),
+    "tlb_add_norm": (_I, [_VP, _VP, _VP, _VP, _F, _VP, _I, _I, _I, _VP]),
+    "tlb_norm_mix2": (_I, [_VP, _VP, _VP, _VP, _F, _F, _VP, _I, _I, _I, _VP]),
+    "tlb_paged_attention_tile_tokens": (_I, [_I, _I]),
+    "tlb_paged_attention": (_I, [_VP, _LL, _LL, _VP, _I, _I, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _F, _I, _VP, _LL, _VP, _LL, _LL, _I, _VP]),
+    "tlb_kv_prepare": (_I, [_VP, _LL, _LL, _I, _VP, _VP, _LL, _LL, _VP, _LL, _LL, _I, _I, _I, _VP, _F, _VP, _VP, _VP, _I, _I, _I, _VP, _I, _I, _VP]),
+    "tlb_decay_scan": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _VP, _F, _F, _I, _I, _I, _VP, _I, _VP, _LL, _I, _VP, _I, _VP]),
+    "tlb_head_norm_gate": (_I, [_VP, _VP, _F, _VP, _LL, _I, _VP, _I, _I, _I, _I, _VP]),
     "tlb_moe_max_rows": (_LL, [_I, _I, _I, _I]),
     "tlb_moe_sort": (_I, [_VP, _I, _I, _I, _I, _VP, _VP, _VP, _VP]),
     "tlb_moe_gate_up": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _VP, _I, _VP]),
@@ -46,10 +55,12 @@ _SIGNATURES = {
 }
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 ATTENTION_TILE_TOKENS = 4
 MOE_TILE_ROWS = 32
-ACT_SILU, ACT_GELU_TANH = 0, 1
+ACT_SILU, ACT_GELU_TANH, ACT_RELU_SQUARED = 0, 1, 2
+MASK_CAUSAL, MASK_WINDOW, MASK_CHUNK = 0, 1, 2
+SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 2}
 
 
@@ -284,25 +295,29 @@ def gated_act(gate_up: torch.Tensor, act: int) -> torch.Tensor:
     return out
 
 
-def moe_route(h, router_w, router_b, top: int):
+def moe_route(h, router_w, router_b, top: int, scoring: int = SCORE_SOFTMAX):
+    """-> (expert ids int32 [T, top], weights fp32 [T, top]): softmax over the chosen logits, or each one's sigmoid."""
     _gpu("moe_route", h, router_w, router_b)
     _contig("moe_route", h, router_w, router_b)
     T, D = h.shape
     E = router_w.shape[0]
     idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
     gate = torch.empty((T, top), dtype=torch.float32, device=h.device)
-    _check(library().tlb_moe_route(_ptr(h), _ptr(router_w), _ptr(router_b), T, D, E, top, _ptr(idx), _ptr(gate), _code(h.dtype), _stream(h)))
+    _check(library().tlb_moe_route(_ptr(h), _ptr(router_w), _ptr(router_b), T, D, E, top, int(scoring), _ptr(idx), _ptr(gate), _code(h.dtype),
+                                   _stream(h)))
     return idx, gate
 
 
-def moe_experts(h, idx, gate, w_gate, w_up, w_down, act: int, shared=None) -> torch.Tensor:
-    """Weighted sum of the chosen experts' gated feed-forwards (+ ``shared [T, D]``) -> fp32 ``[T, D]``.
-    ``w_gate, w_up [E, ff, D]``, ``w_down [E, D, ff]``."""
+def moe_experts(h, idx, gate, w_gate, w_up, w_down, act: int, shared=None, scale_input: bool = False) -> torch.Tensor:
+    """Sum of the chosen experts' feed-forwards (+ ``shared [T, D]``) -> fp32 ``[T, D]``.  ``w_up [E, ff, D]``,
+    ``w_down [E, D, ff]``; with ``w_gate [E, ff, D]`` an expert is ``down(act(gate x) * (up x))``, without it
+    ``down(act(up x))``.  The router's weight multiplies the expert's output, or, ``scale_input``, its input ``x``
+    (rounded to the compute dtype)."""
     _gpu("moe_experts", h, idx, gate, w_gate, w_up, w_down, shared)
     _contig("moe_experts", h, idx, gate, w_gate, w_up, w_down, shared)
     lib = library()
     T, D = h.shape
-    E, ff, _ = w_gate.shape
+    E, ff, _ = w_up.shape
     top = idx.shape[1]
     # 64-row expert tiles once the average expert gets that many rows (tensor-core kernels only: bf16, widths % 8 == 0)
     rows = 64 if (h.dtype == torch.bfloat16 and D % 8 == 0 and ff % 8 == 0 and T * top >= 64 * E) else MOE_TILE_ROWS
@@ -315,11 +330,137 @@ def moe_experts(h, idx, gate, w_gate, w_up, w_down, act: int, shared=None) -> to
     pair_out = torch.empty((T * top, D), dtype=torch.float32, device=dev)
     y = torch.empty((T, D), dtype=torch.float32, device=dev)
     _check(lib.tlb_moe_sort(_ptr(idx), T, top, E, rows, _ptr(sorted_pair), _ptr(tile_expert), _ptr(counters), st))
-    _check(lib.tlb_moe_gate_up(_ptr(h), _ptr(w_gate), _ptr(w_up), _ptr(sorted_pair), _ptr(tile_expert), _ptr(counters), T, top, E, rows, D, ff, act,
-                               _ptr(inter), code, st))
+    rows_in, per_pair = h, 0
+    if scale_input:
+        rows_in, per_pair = torch.empty((T * top, D), dtype=h.dtype, device=dev), 1
+        _check(lib.tlb_moe_scale_rows(_ptr(h), _ptr(gate), _ptr(rows_in), T, top, D, code, st))
+    if w_gate is not None:
+        if per_pair:
+            raise RuntimeError("moe_experts: gated experts take the router's weight on their output")
+        _check(lib.tlb_moe_gate_up(_ptr(h), _ptr(w_gate), _ptr(w_up), _ptr(sorted_pair), _ptr(tile_expert), _ptr(counters), T, top, E, rows, D, ff, act,
+                                   _ptr(inter), code, st))
+    else:
+        _check(lib.tlb_moe_up(_ptr(rows_in), _ptr(w_up), _ptr(sorted_pair), _ptr(tile_expert), _ptr(counters), T, top, E, rows, D, ff, act, per_pair,
+                              _ptr(inter), code, st))
     _check(lib.tlb_moe_down(_ptr(inter), _ptr(w_down), _ptr(sorted_pair), _ptr(tile_expert), _ptr(counters), T, top, E, rows, D, ff, _ptr(pair_out), code, st))
-    _check(lib.tlb_moe_combine(_ptr(pair_out), _ptr(gate), _ptr(shared), _ptr(y), T, top, D, code, st))
+    _check(lib.tlb_moe_combine(_ptr(pair_out), None if scale_input else _ptr(gate), _ptr(shared), _ptr(y), T, top, D, code, st))
     return y
+
+
+def add_norm(residual: torch.Tensor, a: torch.Tensor, b: torch.Tensor | None, weight: torch.Tensor | None, eps: float):
+    """``residual += a (+ b)`` (all fp32 ``[rows, dim]``, in place); with ``weight`` also returns the RMS norm of the new
+    residual times ``weight``, rounded to the weight's dtype."""
+    _gpu("add_norm", residual, a, b, weight)
+    _contig("add_norm", residual, a, b, weight)
+    rows, dim = residual.shape
+    if residual.dtype != torch.float32 or a.dtype != torch.float32 or a.shape != residual.shape or (b is not None and (b.dtype != torch.float32 or b.shape != residual.shape)):
+        raise RuntimeError("add_norm: residual and addends must be float32 of one shape")
+    h = None if weight is None else torch.empty((rows, dim), dtype=weight.dtype, device=residual.device)
+    code = _code(weight.dtype) if weight is not None else 0
+    _check(library().tlb_add_norm(_ptr(residual), _ptr(a), _ptr(b), _ptr(weight), float(eps), _ptr(h), rows, dim, code, _stream(residual)))
+    return h
+
+
+def norm_mix2(a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: torch.Tensor, coef: float, eps: float) -> torch.Tensor:
+    """``coef * (rms_norm(a) * wa + rms_norm(b) * wb)``: fp32 ``[rows, dim]`` in and out."""
+    _gpu("norm_mix2", a, wa, b, wb)
+    _contig("norm_mix2", a, wa, b, wb)
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or a.shape != b.shape or wa.dtype != wb.dtype:
+        raise RuntimeError("norm_mix2: a and b must be float32 of one shape, the weights of one dtype")
+    y = torch.empty_like(a)
+    _check(library().tlb_norm_mix2(_ptr(a), _ptr(wa), _ptr(b), _ptr(wb), float(coef), float(eps), _ptr(y), a.shape[0], a.shape[1], _code(wa.dtype), _stream(a)))
+    return y
+
+
+def paged_attention_tile_tokens(heads: int, kv_heads: int) -> int:
+    """The most tokens an entry of ``tiles`` may hold for ``paged_attention`` with these head counts."""
+    n = int(library().tlb_paged_attention_tile_tokens(heads, kv_heads))
+    if n <= 0:
+        raise RuntimeError(f"paged_attention: {heads} heads do not divide into {kv_heads} key/value heads")
+    return n
+
+
+def kv_prepare(q, k, v, *, q_norm=None, k_norm=None, eps: float = 0.0, tok_pos=None, tok_seq=None, block_table=None, slab=None):
+    """``q [T, H, dk]`` (a view; normed in place when ``q_norm`` is given), ``k [T, G, dk]``, ``v [T, G, dv]`` (views, or
+    None for a layer that reads another layer's cache): optional per-head RMS norms, then keys and values go to every
+    token's slot of ``slab [P, page, G * (dk + dv)]``."""
+    _gpu("kv_prepare", q, k, v, q_norm, k_norm, tok_pos, tok_seq, block_table, slab)
+    T, H, dk = q.shape
+    G = dv = 0
+    if k is not None:
+        G, dv = k.shape[1], v.shape[2]
+        P, page_size, width = slab.shape
+        if k.shape != (T, G, dk) or v.shape[:2] != (T, G) or width != G * (dk + dv) or not (q.dtype == k.dtype == v.dtype == slab.dtype):
+            raise RuntimeError("kv_prepare: keys, values and cache do not match")
+        if k.stride(2) != 1 or v.stride(2) != 1 or not slab.is_contiguous():
+            raise RuntimeError("kv_prepare: unit inner strides wanted")
+    elif q_norm is None:
+        return
+    if q.stride(2) != 1:
+        raise RuntimeError("kv_prepare: unit inner strides wanted")
+    P, page_size = (slab.shape[0], slab.shape[1]) if slab is not None else (0, 0)
+    _check(library().tlb_kv_prepare(_ptr(q), q.stride(0), q.stride(1), H, _ptr(q_norm), _ptr(k), k.stride(0) if k is not None else 0,
+                                    k.stride(1) if k is not None else 0, _ptr(v), v.stride(0) if v is not None else 0, v.stride(1) if v is not None else 0,
+                                    G, dk, max(dv, 1), _ptr(k_norm), float(eps), _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table),
+                                    block_table.shape[1] if block_table is not None else 0, P, page_size, _ptr(slab), T, _code(q.dtype), _stream(q)))
+
+
+def paged_attention(q, slab, block_table, tiles, tok_pos, *, kv_heads: int, dv: int, mask: int, mask_size: int, scale: float, softcap: float = 0.0,
+                    sink: bool = False, gate=None, out=None):
+    """``q [T, H, dk]`` (a view with unit inner stride) against ``slab [P, page, kv_heads * (dk + dv)]`` -> ``out [T, H, dv]``
+    (contiguous, the query's dtype).  ``gate [T, H]`` (a view with unit inner stride): logits of a sigmoid output gate."""
+    _gpu("paged_attention", q, slab, block_table, tiles, tok_pos, gate, out)
+    _contig("paged_attention", slab, block_table, tiles, tok_pos)
+    T, H, dk = q.shape
+    P, page_size, width = slab.shape
+    if width != kv_heads * (dk + dv) or q.dtype != slab.dtype or q.stride(2) != 1:
+        raise RuntimeError("paged_attention: query and cache do not match")
+    if gate is not None and (gate.shape != (T, H) or gate.stride(1) != 1 or gate.dtype != q.dtype):
+        raise RuntimeError("paged_attention: gate must be [T, H] of the query's dtype")
+    if out is None:
+        out = torch.empty((T, H, dv), dtype=q.dtype, device=q.device)
+    _check(library().tlb_paged_attention(_ptr(q), q.stride(0), q.stride(1), _ptr(slab), P, page_size, dk, dv, H, kv_heads, _ptr(block_table),
+                                         block_table.shape[1], _ptr(tiles), tiles.shape[0], _ptr(tok_pos), int(mask), int(mask_size), float(scale),
+                                         float(softcap or 0.0), int(bool(sink)), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out),
+                                         out.stride(0), out.stride(1), _code(q.dtype), _stream(q)))
+    return out
+
+
+def decay_scan(q, k, v, z, z_bias, *, tau: float, q_scale: float, seq_info, state, out=None):
+    """Linear attention with per-channel decay ``sigmoid(z + z_bias)^(1/tau)``: ``q, k [T, H, dk]``, ``v [T, H, dv]`` views,
+    ``z [T, H * dk]`` fp32, ``seq_info [S, 4]`` int32 (first token, count, start position, slot), ``state [slots, H, dk, dv]``
+    fp32 (a view whose slots may be further apart) -> fp32 ``[T, H, dv]``."""
+    _gpu("decay_scan", q, k, v, z, z_bias, seq_info, state, out)
+    T, H, dk = q.shape
+    dv = v.shape[2]
+    if k.shape != (T, H, dk) or v.shape[:2] != (T, H) or z.shape != (T, H * dk) or z.dtype != torch.float32 or z.stride(1) != 1:
+        raise RuntimeError("decay_scan: shapes do not match")
+    if q.stride(2) != 1 or k.stride(2) != 1 or v.stride(2) != 1 or not (q.dtype == k.dtype == v.dtype):
+        raise RuntimeError("decay_scan: unit inner strides and one dtype wanted")
+    if state.dtype != torch.float32 or state.shape[1:] != (H, dk, dv) or not state[0].is_contiguous():
+        raise RuntimeError("decay_scan: state must be float32 [slots, H, dk, dv]")
+    if seq_info.dtype != torch.int32 or seq_info.dim() != 2 or seq_info.shape[1] != 4 or not seq_info.is_contiguous():
+        raise RuntimeError("decay_scan: seq_info must be int32 [S, 4]")
+    if out is None:
+        out = torch.empty((T, H, dv), dtype=torch.float32, device=q.device)
+    _check(library().tlb_decay_scan(_ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1), _ptr(v), v.stride(0), v.stride(1), _ptr(z),
+                                    z.stride(0), _ptr(z_bias), float(tau), float(q_scale), H, dk, dv, _ptr(seq_info), seq_info.shape[0], _ptr(state),
+                                    state.stride(0), state.shape[0], _ptr(out), _code(q.dtype), _stream(q)))
+    return out
+
+
+def head_norm_gate(o, weight, eps: float, gate=None, act: int = 1):
+    """``o [T, H, dv]`` fp32 -> ``[T, H * dv]`` in the weight's dtype: per-head RMS norm times ``weight [dv]`` times
+    ``silu(gate)`` (``act`` 1) or ``gate`` (0); ``gate [T, H * dv]`` a view with unit inner stride."""
+    _gpu("head_norm_gate", o, weight, gate)
+    _contig("head_norm_gate", o, weight)
+    T, H, dv = o.shape
+    if o.dtype != torch.float32 or weight.shape != (dv,) or (gate is not None and (gate.shape != (T, H * dv) or gate.stride(1) != 1 or gate.dtype != weight.dtype)):
+        raise RuntimeError("head_norm_gate: shapes do not match")
+    out = torch.empty((T, H * dv), dtype=weight.dtype, device=o.device)
+    _check(library().tlb_head_norm_gate(_ptr(o), _ptr(weight), float(eps), _ptr(gate), gate.stride(0) if gate is not None else 0, int(act), _ptr(out),
+                                        T, H, dv, _code(weight.dtype), _stream(o)))
+    return out
 
 
 def argmax_rows(logits: torch.Tensor) -> torch.Tensor:

@@ -16,7 +16,10 @@ MODEL_SHORTCUTS = {
 # Designs that describe themselves in config.json (key "architecture"): name -> class with
 # ``from_checkpoint(config, tensors, dtype=, device=, **kwargs)``.  Imported on demand: a process that runs one design
 # loads (and, for the native libraries, builds) only what that design uses.
-ARCHITECTURES = {"Voluzen": ("tiny_llm_b200.voluzen", "VoluzenModel")}
+ARCHITECTURES = {
+    "Voluzen": ("tiny_llm_b200.voluzen", "VoluzenModel"),
+    "Bapovik": ("tiny_llm_b200.bapovik", "BapovikModel"),
+}
 
 
 def model_class(architecture: str):

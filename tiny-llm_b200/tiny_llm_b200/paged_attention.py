@@ -1,0 +1,85 @@
+"""Grouped-query softmax attention over the paged cache of a ragged batch, with the choices a design may make as
+parameters: what a position sees (``mask`` = ``"causal"``, ``"window"``: itself and the ``mask_size - 1`` positions
+before it, ``"chunk"``: the earlier positions of its own block of ``mask_size`` positions counted from 0), a tanh
+``softcap`` on the scaled scores, a ``sink`` (one more term ``exp(0)`` in the softmax's denominator), per-head RMS
+norms of queries and keys (plain weights of size ``dim``, shared by the heads) and a sigmoid output gate per head.
+Positions do not enter the scores (no rotation).
+
+The layer's input projections are made by the caller in one product (``FusedProjection``); the module takes the views
+``q [T, H * dim]``, ``k [T, G * dim]``, ``v [T, G * vdim]`` and ``gate [T, H]`` (logits), stores keys and values in the
+layer's slab ``[pages, page_size, G * (dim + vdim)]`` (or, built with ``caches=False``, reads another layer's slab and
+gets no k / v), runs the attention kernel over the plan's work list and returns the output projection in fp32.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .basics import linear, linear_wide
+
+MASKS = {"causal": 0, "window": 1, "chunk": 2}
+
+
+class FusedProjection:
+    """Several projections of one input as ONE product: the weights stacked by rows (padded to a multiple of 8 rows), the
+    biases, where any part has one, stacked likewise; ``proj(h)[name]`` is that part's columns of the result."""
+
+    def __init__(self, parts: list, dtype, device):
+        self.spans, rows, biases, at = {}, [], [], 0
+        for name, weight, bias in parts:
+            n = weight.shape[0]
+            self.spans[name] = (at, n)
+            rows.append(weight)
+            biases.append(bias if bias is not None else torch.zeros(n, dtype=weight.dtype, device=weight.device))
+            at += n
+        pad = -at % 8
+        if pad:
+            rows.append(torch.zeros((pad, rows[0].shape[1]), dtype=rows[0].dtype, device=rows[0].device))
+            biases.append(torch.zeros(pad, dtype=rows[0].dtype, device=rows[0].device))
+        self.weight = torch.cat(rows, dim=0).to(device=device, dtype=dtype).contiguous()
+        self.bias = torch.cat(biases).to(device=device, dtype=dtype).contiguous() if any(b is not None for _, _, b in parts) else None
+
+    def __call__(self, h: torch.Tensor) -> dict:
+        y = linear(h, self.weight) if self.bias is None else torch.addmm(self.bias, h, self.weight.t())
+        return {name: y[:, at : at + n] for name, (at, n) in self.spans.items()}
+
+
+class PagedGroupedAttention:
+    def __init__(self, *, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, mask: str, mask_size: int, w_o, softcap: float | None = None,
+                 sink: bool = False, q_norm=None, k_norm=None, eps: float = 1e-6, caches: bool = True):
+        if heads % kv_heads:
+            raise ValueError(f"{heads} query heads do not divide into {kv_heads} key/value heads")
+        if mask not in MASKS or (mask != "causal" and int(mask_size) <= 0):
+            raise ValueError(f"mask {mask!r} of size {mask_size}")
+        if tuple(w_o.shape)[1] != heads * vdim:
+            raise ValueError("attention: the output projection does not match heads x vdim")
+        self.heads, self.kv_heads, self.dim, self.vdim = int(heads), int(kv_heads), int(dim), int(vdim)
+        self.scale, self.mask, self.mask_size = float(scale), MASKS[mask], int(mask_size or 0)
+        self.softcap, self.sink, self.eps, self.caches = float(softcap or 0.0), bool(sink), float(eps), bool(caches)
+        self.q_norm = None if q_norm is None else q_norm.contiguous()
+        self.k_norm = None if k_norm is None else k_norm.contiguous()
+        self.w_o = w_o.contiguous()
+
+    @property
+    def cache_width(self) -> int:
+        return self.kv_heads * (self.dim + self.vdim)
+
+    @property
+    def tile_tokens(self) -> int:
+        from extensions_b200.tiny_llm_ext_b200 import blocks
+
+        return blocks.paged_attention_tile_tokens(self.heads, self.kv_heads)
+
+    def __call__(self, q, k, v, gate, plan, slab: torch.Tensor) -> torch.Tensor:
+        from extensions_b200.tiny_llm_ext_b200 import blocks
+
+        T, H, G = q.shape[0], self.heads, self.kv_heads
+        q3 = q.unflatten(1, (H, self.dim))
+        if self.caches:
+            blocks.kv_prepare(q3, k.unflatten(1, (G, self.dim)), v.unflatten(1, (G, self.vdim)), q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps,
+                              tok_pos=plan.tok_pos, tok_seq=plan.tok_seq, block_table=plan.block_table, slab=slab)
+        elif self.q_norm is not None:
+            blocks.kv_prepare(q3, None, None, q_norm=self.q_norm, eps=self.eps)
+        o = blocks.paged_attention(q3, slab, plan.block_table, plan.tiles_for(self.tile_tokens), plan.tok_pos, kv_heads=G, dv=self.vdim, mask=self.mask,
+                                   mask_size=self.mask_size, scale=self.scale, softcap=self.softcap, sink=self.sink, gate=gate)
+        return linear_wide(o.view(T, H * self.vdim), self.w_o)  # fp32: a norm or the residual sum reads it unrounded

@@ -4,11 +4,13 @@ A continuous-batching step is a flat list of tokens: a portion of one request's 
 others.  ``RaggedEntry`` names one request's share, ``RaggedPlan`` is what the kernels need, built on the host from the
 requests' page lists and moved to the device as ONE pinned block:
 
-    ids [T] | tok_pos [T] | tok_seq [T] | want_rows [W] | block_table [S, max_pages] | tiles [n, 3] per tile size
+    ids [T] | tok_pos [T] | tok_seq [T] | want_rows [W] | block_table [S, max_pages] | tiles [n, 3] per tile size | seq_info [S, 4]
 
 ``tok_pos`` is the position of a token in its sequence, ``tok_seq`` its row in this step's block table, ``tiles`` the
 attention kernels' work lists (runs of at most ``tile`` consecutive tokens of one sequence; one list per tile size
-the model's layers ask for, ``tiles_for(size)``).  Building the plan also
+the model's layers ask for, ``tiles_for(size)``), ``seq_info`` one row per sequence for kernels that walk a sequence's new
+tokens in order (first flat token, token count, position of the first token, the request's recurrent-state slot or -1).
+Building the plan also
 does the step's cache bookkeeping: every request's page list grows by its new tokens (pages come from the pool's free
 list first), before anything is launched.
 """
@@ -30,6 +32,11 @@ class RaggedEntry:
 
 
 class RaggedPlan:
+    @staticmethod
+    def block_ints(tokens: int, wanted: int, seqs: int, max_pages: int, tiles: int) -> int:
+        """Number of int32 in a plan's device block (``tiles`` summed over the tile sizes)."""
+        return 3 * tokens + wanted + seqs * max_pages + 3 * tiles + 4 * seqs
+
     def __init__(self, entries: Sequence[RaggedEntry], device, tile, max_pages: int | None = None, into: torch.Tensor | None = None):
         """``max_pages`` fixes the block table's width (at least what the longest request needs) and ``into`` names a
         preallocated int32 device block to upload into: a captured graph reads the same addresses every step."""
@@ -63,7 +70,7 @@ class RaggedPlan:
         wants = [list(e.want) if e.want is not None else [len(e.tokens) - 1] for e in entries]
         W = sum(len(w) for w in wants)
         n_tiles = {size: sum(-(-len(e.tokens) // size) for e in entries) for size in sizes}
-        total = 3 * T + W + S * max_pages + 3 * sum(n_tiles.values())
+        total = self.block_ints(T, W, S, max_pages, sum(n_tiles.values()))
         host = torch.empty(max(total, 1), dtype=torch.int32, pin_memory=torch.cuda.is_available() and torch.device(device).type == "cuda")
         buf = host.numpy()
         ids, pos, seq = buf[0:T], buf[T : 2 * T], buf[2 * T : 3 * T]
@@ -74,6 +81,7 @@ class RaggedPlan:
         for size in sizes:
             tile_at[size] = (at, n_tiles[size])
             at += 3 * n_tiles[size]
+        info = buf[at : at + 4 * S].reshape(S, 4)
         tile_rows = {size: [] for size in sizes}
         t = w = 0
         for s, (e, o, start) in enumerate(zip(entries, owners, starts)):
@@ -89,6 +97,7 @@ class RaggedPlan:
             for size in sizes:
                 tile_rows[size] += [(t + first, min(size, n - first), s) for first in range(0, n, size)]
             table[s, : o.num_pages] = o.page_ids
+            info[s] = (t, n, start, getattr(o, "state_slot", -1))
             t += n
         for size in sizes:
             start, n = tile_at[size]
@@ -108,10 +117,15 @@ class RaggedPlan:
         self.want_rows = dev[3 * T : 3 * T + W]
         self.block_table = dev[3 * T + W : 3 * T + W + S * max_pages].view(S, max_pages)
         self._tiles = {size: dev[start : start + 3 * n].view(n, 3) for size, (start, n) in tile_at.items()}
+        self.seq_info = dev[at : at + 4 * S].view(S, 4)
         self.tiles = self._tiles[sizes[0]]
         self.max_context = max(o.offset for o in owners)  # the longest sequence after this step's append
         self.want_counts = [len(x) for x in wants]
         self.starts = starts
+        self.owners = owners
+        for o in owners:  # from here on the step runs: what it consumes cannot be taken back from a recurrent state
+            if hasattr(o, "ran_offset"):
+                o.ran_offset = o.offset
 
     def tiles_for(self, size: int) -> torch.Tensor:
         """The work list cut into runs of at most ``size`` tokens (one of the sizes the plan was built for)."""

@@ -269,3 +269,79 @@ def save_voluzen(config: dict, tensors: dict, path) -> None:
     path.mkdir(parents=True, exist_ok=True)
     (path / "config.json").write_text(json.dumps(config, indent=1))
     save_file({k: v.contiguous() for k, v in tensors.items()}, str(path / "model.safetensors"))
+
+
+# ---- Bapovik (windowed / chunked attention beside a recurrent mixer, experts; bapovik.py) ---------------------
+def bapovik_config(*, width=96, vocab=200, pattern="APSP", heads=4, kv_heads=2, dim=16, vdim=24, window=20, chunk=28, softcap=30.0,
+                   rec_heads=2, rec_dim=16, rec_vdim=32, tau=8.0, experts=6, top=2, expert_ff=40, eps=1e-5) -> dict:
+    """A config.json for a stack spelled by ``pattern``, one letter a layer: ``A`` sliding-window attention with experts,
+    ``a`` the same without a feed-forward, ``S`` window attention reading the keys and values of the nearest ``A`` / ``a``
+    layer before it, ``P`` a parallel layer (chunked attention beside the recurrent mixer) with experts, ``p`` one
+    without a feed-forward."""
+    layers, last = [], None
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff}}
+    for i, letter in enumerate(pattern):
+        if letter in "AaS":
+            mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": float(dim ** -0.5), "mask": {"size": window}}
+            if letter == "S":
+                if last is None:
+                    raise ValueError("'S' needs an attention layer with its own keys and values before it")
+                mixer["kv_from"] = last
+            else:
+                last = i
+            layers.append({"type": "attention", "mixer": mixer, "mlp": None if letter == "a" else moe})
+        elif letter in "Pp":
+            left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": float(dim ** -0.5), "mask": {"size": chunk}, "softcap": softcap}
+            right = {"heads": rec_heads, "dim": rec_dim, "vdim": rec_vdim, "tau": tau}
+            layers.append({"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": None if letter == "p" else moe})
+        else:
+            raise ValueError(f"unknown layer letter {letter!r}")
+    return {"architecture": "Bapovik", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+
+
+def synthetic_bapovik(config: dict, seed: int = 0, dtype=torch.bfloat16) -> dict:
+    """Random tensors for ``config`` under the checkpoint's names (CPU, seeded)."""
+    gen = torch.Generator().manual_seed(seed)
+    D = config["width"]
+
+    def mat(out_dim, in_dim, gain=1.0):
+        return (torch.randn(out_dim, in_dim, generator=gen) * (gain / in_dim**0.5)).to(dtype)
+
+    def vec(n, centre, spread):
+        return (centre + spread * torch.randn(n, generator=gen)).to(dtype)
+
+    tensors = {"embed": torch.randn(config["vocab"], D, generator=gen).to(dtype), "final.norm": vec(D, 1.0, 0.1), "head": mat(config["vocab"], D)}
+
+    def attention(p, m):
+        H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        tensors[p + "q"], tensors[p + "q.b"] = mat(H * dk, D, 2.0), vec(H * dk, 0.0, 0.2)
+        if m.get("kv_from") is None:
+            tensors[p + "k"], tensors[p + "k.b"] = mat(G * dk, D, 2.0), vec(G * dk, 0.0, 0.2)
+            tensors[p + "v"], tensors[p + "v.b"] = mat(G * dv, D), vec(G * dv, 0.0, 0.2)
+        tensors[p + "g"], tensors[p + "o"] = mat(H, D, 2.0), mat(D, H * dv)
+
+    for i, layer in enumerate(config["layers"]):
+        m, p = layer["mixer"], f"l{i}."
+        tensors[p + "norm1"] = vec(D, 1.0, 0.1)
+        if layer["type"] == "attention":
+            attention(p + "mix.", m)
+        else:
+            attention(p + "mix.left.", m["left"])
+            dk = m["left"]["dim"]
+            tensors[p + "mix.left.q.norm"], tensors[p + "mix.left.k.norm"] = vec(dk, 1.0, 0.2), vec(dk, 1.0, 0.2)
+            r, rp = m["right"], p + "mix.right."
+            H, dk, dv = r["heads"], r["dim"], r["vdim"]
+            low = max(4, H * dk // 8)
+            tensors[rp + "q"], tensors[rp + "k"], tensors[rp + "v"] = mat(H * dk, D, 2.0), mat(H * dk, D, 2.0), mat(H * dv, D)
+            tensors[rp + "g"], tensors[rp + "o"], tensors[rp + "norm"] = mat(H * dv, D), mat(D, H * dv), vec(dv, 1.0, 0.2)
+            tensors[rp + "a1"], tensors[rp + "a2"], tensors[rp + "a2.b"] = mat(low, D), mat(H * dk, low, 2.0), vec(H * dk, 2.0, 1.0)
+            tensors[p + "mix.left.out"], tensors[p + "mix.right.out"] = vec(D, 1.0, 0.2), vec(D, 1.0, 0.2)
+        mlp = layer.get("mlp")
+        if mlp:
+            tensors[p + "mlp.router"] = mat(mlp["router"]["experts"], D, 2.0)
+            for k in range(mlp["router"]["experts"]):
+                tensors[p + f"mlp.e{k}.up"], tensors[p + f"mlp.e{k}.down"] = mat(mlp["expert"]["ff"], D, 1.5), mat(D, mlp["expert"]["ff"])
+    return tensors
+
+
+save_bapovik = save_voluzen  # the same directory layout: config.json + model.safetensors

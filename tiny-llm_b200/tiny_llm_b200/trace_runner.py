@@ -6,7 +6,8 @@ Every input line is one engine step, ``{"step": n, "entries": [{"id", "tokens", 
 entries run as ONE ragged batch through the model's own step (``forward_ragged``), portions of prompts beside single
 tokens, on top of whatever earlier steps left in the paged cache.  A request is admitted into a free slot of the
 scheduler's slot tables at its first entry and gives its pages back when it is listed under ``end``.  The page pool
-is sized once, for ``--max-tokens`` tokens (rounded up to whole pages), so pages are reused as requests come and go.
+is sized once, for ``--max-tokens`` tokens (rounded up to whole pages), and a model with recurrent layers gets as many
+state slots as there are request slots, so pages and state slots are reused as requests come and go.
 For a step with wanted places the fp32 logits ``[wanted, vocab]`` go to ``<out>/<step>.f32`` (little-endian); after
 every step the line ``done <step>`` is printed.  Nothing is sampled.
 """
@@ -38,7 +39,7 @@ def main(argv=None) -> int:
     from .ragged import RaggedEntry
 
     dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[args.dtype]
-    model = load_model(args.model, device=args.device, dtype=dtype, page_size=args.page_size, max_tokens=args.max_tokens)
+    model = load_model(args.model, device=args.device, dtype=dtype, page_size=args.page_size, max_tokens=args.max_tokens, max_requests=SLOTS)
     if not hasattr(model, "forward_ragged"):
         print(f"{type(model).__name__} has no ragged step", file=sys.stderr)
         return 4
