@@ -12,8 +12,6 @@ key/value heads, ``dk`` query/key and ``dv`` value entries per head.
 
 from __future__ import annotations
 
-import math
-
 import torch
 
 
@@ -39,6 +37,8 @@ def visible(i: int, j: int, kind: str, size: int) -> bool:
     ``chunk``: earlier positions of its own block of ``size`` positions counted from 0."""
     if j > i:
         return False
+    if kind == "causal":
+        return True
     if kind == "window":
         return i - j < size
     if kind == "chunk":
@@ -172,3 +172,13 @@ def forward(tokens, weights, config, dtype=torch.float64, trace=None):
             trace.append(x.clone())
     x = norm_plain(x, weights["final.norm"].to(dtype), config["norm"]["eps"])
     return x @ weights["head"].to(dtype).T
+
+
+def greedy(tokens, weights, config, new: int, dtype=torch.float64) -> list:
+    """``new`` greedy tokens after the prompt, by recomputing the whole sequence for each."""
+    ids, out = list(tokens), []
+    for _ in range(new):
+        nxt = int(forward(ids, weights, config, dtype=dtype)[-1].argmax())
+        out.append(nxt)
+        ids.append(nxt)
+    return out

@@ -1,0 +1,508 @@
+"""Bapovik on a B200 against the plain CPU restatement (oracle/bapovik.py, float64): each mechanism of the blocks
+library alone, then the model through every way of cutting and batching a sequence, the schedulers and the entry
+points.  Small made-up configurations and random weights; where random weights would hide a fault (one far key among
+hundreds, an edge of a window or a chunk, a sink) the inputs are built so that one score stands out.
+
+Tolerances: relative root-mean-square error of a logits row (mean taken off) below 5e-5 in float32 mode - every product
+in true fp32, so only summation order differs.  In bfloat16 mode a router's close call can go the other way for a token
+(its row then differs by more than rounding), so whole schedules are held to a median of 3e-2, 95 % of the rows below
+1.5e-1; the float32 run is the sharp test.
+"""
+
+import pytest
+import torch
+
+from oracle import bapovik as O
+from extensions_b200.tiny_llm_ext_b200 import blocks
+from tiny_llm_b200 import BatchingKvCache, ContinuousBatcher, greedy_generate_ids
+from tiny_llm_b200.models import load_model, model_class
+from tiny_llm_b200.ragged import RaggedEntry, RaggedPlan
+from tiny_llm_b200.synthetic import bapovik_config, save_bapovik, synthetic_bapovik
+
+pytestmark = pytest.mark.gpu
+
+MASK = {"causal": blocks.MASK_CAUSAL, "window": blocks.MASK_WINDOW, "chunk": blocks.MASK_CHUNK}
+
+
+@pytest.fixture(scope="module")
+def dev(cuda_device):
+    return cuda_device
+
+
+def row_errors(got, want):
+    d = got.double().cpu() - want.double()
+    d = d - d.mean(-1, keepdim=True)
+    w = want.double() - want.double().mean(-1, keepdim=True)
+    return d.pow(2).mean(-1).sqrt() / w.pow(2).mean(-1).sqrt().clamp_min(1e-9)
+
+
+def row_error(got, want):
+    return row_errors(got, want).max().item()
+
+
+def rows_match(got, want, dtype):
+    err = row_errors(got, want)
+    if dtype == torch.float32:
+        return err.max().item() < 5e-5
+    return err.median().item() < 3e-2 and err.quantile(0.95).item() < 1.5e-1
+
+
+def close(got, want, tol):
+    got, want = got.double().cpu(), want.double()
+    err = (got - want).abs().max().item()
+    scale = want.abs().max().item() + 1e-9
+    assert err <= tol * scale, (err, scale)
+
+
+def ids_for(n, vocab, seed):
+    return torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+class Paged:
+    """One sequence's keys and values in a slab whose pages are deliberately out of order, with the plan's integers."""
+
+    def __init__(self, dev, dtype, k, v, page_size=32, spare=3, seed=0):
+        S, G, dk = k.shape
+        dv = v.shape[2]
+        pages = -(-S // page_size)
+        order = torch.randperm(pages + spare, generator=torch.Generator().manual_seed(seed))[:pages]
+        slab = torch.full((pages + spare, page_size, G * (dk + dv)), 7.0, dtype=dtype)  # stale rows must never be read as keys
+        rows = torch.cat([k.reshape(S, G * dk), v.reshape(S, G * dv)], dim=1).to(dtype)
+        for p in range(pages):
+            n = min(page_size, S - p * page_size)
+            slab[order[p], :n] = rows[p * page_size : p * page_size + n]
+        self.slab = slab.to(dev)
+        self.table = order.to(torch.int32).reshape(1, -1).to(dev)
+
+    def tiles(self, dev, first_pos, count, tile):
+        rows = [(t, min(tile, count - t), 0) for t in range(0, count, tile)]
+        pos = torch.arange(first_pos, first_pos + count, dtype=torch.int32)
+        return torch.tensor(rows, dtype=torch.int32).to(dev), pos.to(dev)
+
+
+# ---------------------------------------------------------------------------------------------- mechanisms alone
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dk,dv", [(4, 4, 16, 16), (6, 2, 24, 40), (8, 1, 8, 72), (2, 2, 64, 33)])
+@pytest.mark.parametrize("kind,size,softcap,sink", [("causal", 0, 0.0, False), ("window", 37, 0.0, False), ("chunk", 50, 4.0, True), ("window", 1, 2.0, True)])
+def test_paged_attention_against_plain_attention(dev, dtype, heads, kv_heads, dk, dv, kind, size, softcap, sink):
+    g = torch.Generator().manual_seed(heads * dk + size)
+    S = 150
+    q, k, v = torch.randn(S, heads, dk, generator=g), torch.randn(S, kv_heads, dk, generator=g), torch.randn(S, kv_heads, dv, generator=g)
+    gate = torch.randn(S, heads, generator=g)
+    q, k, v, gate = (t.to(dtype) for t in (q, k, v, gate))
+    want = O.masked_attention(q.double(), k.double(), v.double(), scale=0.4, kind=kind, size=size, softcap=softcap or None, sink=sink)
+    want = want * torch.sigmoid(gate.double())[:, :, None]
+    cache = Paged(dev, dtype, k, v)
+    tile = blocks.paged_attention_tile_tokens(heads, kv_heads)
+    tiles, pos = cache.tiles(dev, 0, S, tile)
+    got = blocks.paged_attention(q.to(dev), cache.slab, cache.table, tiles, pos, kv_heads=kv_heads, dv=dv, mask=MASK[kind], mask_size=size, scale=0.4,
+                                 softcap=softcap, sink=sink, gate=gate.to(dev))
+    close(got, want, 2e-6 if dtype == torch.float32 else 1.5e-2)
+    # the last 9 tokens alone, as a portion that starts in the middle of a page, a window and a chunk: the same rows
+    tiles, pos = cache.tiles(dev, S - 9, 9, tile)
+    part = blocks.paged_attention(q[S - 9 :].to(dev), cache.slab, cache.table, tiles, pos, kv_heads=kv_heads, dv=dv, mask=MASK[kind], mask_size=size,
+                                  scale=0.4, softcap=softcap, sink=sink, gate=gate[S - 9 :].to(dev))
+    assert torch.equal(part, got[S - 9 :])
+
+
+@pytest.mark.parametrize("kind,size", [("window", 70), ("window", 64), ("chunk", 70), ("chunk", 64), ("causal", 0)])
+def test_one_key_that_matters_far_away_at_page_borders_and_mask_edges(dev, kind, size):
+    """All keys are noise but one, which the probing query scores far above the rest: the output is that key's value
+    exactly when the mask lets the query see it.  Prompt rows and single decoded tokens, page size 32."""
+    g = torch.Generator().manual_seed(size)
+    S, dk, dv = 400, 16, 8
+    for target in (0, 31, 32, 63, 64, 200, 329, 330, 331, 398, 399):
+        k, v = 0.05 * torch.randn(S, 1, dk, generator=g), torch.randn(S, 1, dv, generator=g)
+        k[target, 0, 3] = 40.0
+        v[target] = 5.0
+        q = torch.zeros(S, 2, dk)
+        q[:, :, 3] = 1.0
+        cache = Paged(dev, torch.float32, k, v, seed=target)
+        tile = blocks.paged_attention_tile_tokens(2, 1)
+        tiles, pos = cache.tiles(dev, 0, S, tile)
+        whole = blocks.paged_attention(q.to(dev), cache.slab, cache.table, tiles, pos, kv_heads=1, dv=dv, mask=MASK[kind], mask_size=size, scale=1.0).cpu()
+        for i in sorted({target, target + 1, target + size - 2, target + size - 1, target + size, target + size + 1, (target // max(size, 1) + 1) * max(size, 1) - 1,
+                         (target // max(size, 1) + 1) * max(size, 1), S - 1}):
+            if not 0 <= i < S:
+                continue
+            sees = O.visible(i, target, kind, size)
+            assert (whole[i, 0] - 5.0).abs().max().item() < 1e-3 if sees else (whole[i, 0] - 5.0).abs().min().item() > 1.0, (target, i)
+            tiles1, pos1 = cache.tiles(dev, i, 1, tile)  # the same position as a single decoded token
+            one = blocks.paged_attention(q[i : i + 1].to(dev), cache.slab, cache.table, tiles1, pos1, kv_heads=1, dv=dv, mask=MASK[kind], mask_size=size,
+                                         scale=1.0).cpu()
+            assert torch.equal(one[0], whole[i])
+
+
+def test_a_sink_takes_its_share_and_a_soft_cap_bounds_the_scores(dev):
+    """One visible key of score s: without a sink the output is its value; with one it is value * e^s / (1 + e^s), and
+    with a cap c the score is c tanh(s / c)."""
+    k, v = torch.zeros(1, 1, 8), torch.full((1, 1, 4), 3.0)
+    k[0, 0, 0] = 1.0
+    cache = Paged(dev, torch.float32, k, v)
+    tiles, pos = cache.tiles(dev, 0, 1, 16)
+    for s, cap in ((0.0, 0.0), (2.0, 0.0), (-3.0, 0.0), (100.0, 5.0), (0.7, 1.0)):
+        q = torch.zeros(1, 1, 8)
+        q[0, 0, 0] = s
+        run = lambda sink: blocks.paged_attention(q.to(dev), cache.slab, cache.table, tiles, pos, kv_heads=1, dv=4, mask=blocks.MASK_CHUNK, mask_size=5,
+                                                  scale=1.0, softcap=cap, sink=sink).cpu()
+        eff = torch.tensor(cap * torch.tanh(torch.tensor(s / cap)).item() if cap else s, dtype=torch.float64)
+        assert (run(False) - 3.0).abs().max() < 1e-6
+        assert (run(True).double() - 3.0 * torch.sigmoid(eff)).abs().max() < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("normed", [False, True])
+def test_keys_and_values_land_on_their_slots_with_per_head_norms(dev, dtype, normed):
+    g = torch.Generator().manual_seed(5)
+    T, H, G, dk, dv, page = 9, 4, 2, 24, 40, 32
+    q, k, v = (torch.randn(T, n, generator=g).to(dtype) for n in (H * dk, G * dk, G * dv))
+    qn, kn = (1 + 0.3 * torch.randn(dk, generator=g)).to(dtype), (1 + 0.3 * torch.randn(dk, generator=g)).to(dtype)
+    slab = torch.zeros((4, page, G * (dk + dv)), dtype=dtype, device=dev)
+    pos = torch.tensor([30, 31, 32, 33, 34, 0, 1, 63, 64], dtype=torch.int32)   # sequence 0: positions 30..34, sequence 1: 0, 1, sequence 2: 63, 64
+    seq = torch.tensor([0, 0, 0, 0, 0, 1, 1, 2, 2], dtype=torch.int32)
+    table = torch.tensor([[3, 1, -1], [0, -1, -1], [9, 2, 0]], dtype=torch.int32)  # page 9 does not exist: position 63 of sequence 2 is dropped
+    qd = q.to(dev).clone()
+    blocks.kv_prepare(qd.view(T, H, dk), k.to(dev).view(T, G, dk), v.to(dev).view(T, G, dv), q_norm=qn.to(dev) if normed else None,
+                      k_norm=kn.to(dev) if normed else None, eps=1e-5, tok_pos=pos.to(dev), tok_seq=seq.to(dev), block_table=table.to(dev), slab=slab)
+    tol = 1e-6 if dtype == torch.float32 else 8e-3
+    want_q = O.norm_plain(q.double().view(T, H, dk), qn.double(), 1e-5) if normed else q.double().view(T, H, dk)
+    close(qd.view(T, H, dk), want_q, tol)
+    want_k = O.norm_plain(k.double().view(T, G, dk), kn.double(), 1e-5) if normed else k.double().view(T, G, dk)
+    for t, (page_id, slot) in enumerate([(3, 30), (3, 31), (1, 0), (1, 1), (1, 2), (0, 0), (0, 1), None, (2, 0)]):
+        if page_id is None:
+            continue
+        row = slab[page_id, slot].cpu()
+        close(row[: G * dk].view(G, dk), want_k[t], tol)
+        assert torch.equal(row[G * dk :], v[t])
+    assert float(slab[0, 2:].abs().max()) == 0.0 and float(slab[2, 1:].abs().max()) == 0.0  # nothing else was touched
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,dk,dv", [(2, 16, 32), (3, 12, 40), (1, 128, 64), (2, 33, 7)])
+def test_decay_scan_against_the_recurrence_in_portions_batches_and_reused_slots(dev, dtype, heads, dk, dv):
+    g = torch.Generator().manual_seed(dk)
+    lens = [70, 5, 33]
+    T = sum(lens)
+    q, k, v = (torch.randn(T, heads, n, generator=g).to(dtype) for n in (dk, dk, dv))
+    z, zb, tau = 2 * torch.randn(T, heads * dk, generator=g), (1 + torch.randn(heads * dk, generator=g)).to(dtype), 3.0
+    alpha = torch.sigmoid(z.double() + zb.double()).pow(1 / tau).view(T, heads, dk)
+    want, at = [], 0
+    for n in lens:
+        s = slice(at, at + n)
+        want.append(O.decayed_linear_attention(q[s].double() * dk ** -0.5, k[s].double(), v[s].double(), alpha[s]))
+        at += n
+    want = torch.cat(want)
+    tol = 2e-5  # in both modes: the inputs are rounded before the oracle sees them, the recurrence itself is fp32
+    pool = torch.full((5, 3 + heads * dk * dv + 2), 9.0, device=dev)  # slots are wider than this layer's share and hold stale numbers
+    state = pool[:, 3 : 3 + heads * dk * dv].unflatten(1, (heads, dk, dv))
+    whole = blocks.decay_scan(q.to(dev), k.to(dev), v.to(dev), z.to(dev), zb.to(dev), tau=tau, q_scale=dk ** -0.5,
+                              seq_info=torch.tensor([(0, 70, 0, 4), (70, 5, 0, 0), (75, 33, 0, 2)], dtype=torch.int32).to(dev), state=state)
+    close(whole, want, tol)  # the slots' stale 9.0s were ignored at position 0
+    # the first two sequences again in portions, [40 | 2] then [3 | 30], in other slots and another order
+    first = blocks.decay_scan(torch.cat([q[0:40], q[70:72]]).to(dev), torch.cat([k[0:40], k[70:72]]).to(dev), torch.cat([v[0:40], v[70:72]]).to(dev),
+                              torch.cat([z[0:40], z[70:72]]).to(dev), zb.to(dev), tau=tau, q_scale=dk ** -0.5,
+                              seq_info=torch.tensor([(0, 40, 0, 1), (40, 2, 0, 3)], dtype=torch.int32).to(dev), state=state)
+    second = blocks.decay_scan(torch.cat([q[72:75], q[40:70]]).to(dev), torch.cat([k[72:75], k[40:70]]).to(dev), torch.cat([v[72:75], v[40:70]]).to(dev),
+                               torch.cat([z[72:75], z[40:70]]).to(dev), zb.to(dev), tau=tau, q_scale=dk ** -0.5,
+                               seq_info=torch.tensor([(0, 3, 2, 3), (3, 30, 40, 1)], dtype=torch.int32).to(dev), state=state)
+    assert torch.equal(torch.cat([first[:40], second[3:]]), whole[:70]) and torch.equal(torch.cat([first[40:], second[:3]]), whole[70:75])
+    assert float(pool[:, :3].min()) == 9.0 and float(pool[:, -2:].min()) == 9.0  # the neighbours' columns are untouched
+    # token by token from a slot that another sequence used
+    rows = [blocks.decay_scan(q[t : t + 1].to(dev), k[t : t + 1].to(dev), v[t : t + 1].to(dev), z[t : t + 1].to(dev), zb.to(dev), tau=tau, q_scale=dk ** -0.5,
+                              seq_info=torch.tensor([(0, 1, t - 75, 1)], dtype=torch.int32).to(dev), state=state) for t in range(75, 108)]
+    assert torch.equal(torch.cat(rows), whole[75:])
+
+
+def test_a_far_token_survives_in_the_state_only_as_much_as_the_decay_lets_it(dev):
+    """One early token writes the state, 300 silent tokens follow: the probe at the end reads alpha^300 of it."""
+    T, dk, dv = 302, 8, 4
+    q, k, v = torch.zeros(T, 1, dk), torch.zeros(T, 1, dk), torch.zeros(T, 1, dv)
+    k[1, 0, 2], v[1, 0] = 1.0, torch.tensor([1.0, 2.0, 3.0, 4.0])
+    q[-1, 0, 2] = 1.0
+    z = torch.full((T, dk), 3.0)
+    state = torch.zeros((1, 1, dk, dv), device=dev)
+    out = blocks.decay_scan(q.to(dev), k.to(dev), v.to(dev), z.to(dev), None, tau=4.0, q_scale=1.0, seq_info=torch.tensor([(0, T, 0, 0)], dtype=torch.int32).to(dev),
+                            state=state).cpu()
+    keep = torch.sigmoid(torch.tensor(3.0, dtype=torch.float64)).pow(300 / 4.0)
+    close(out[-1, 0], keep * v[1, 0].double(), 1e-4)
+    assert float(out[:-1].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_row_kernels_of_the_layer(dev, dtype):
+    g = torch.Generator().manual_seed(11)
+    T, D, H, dv = 6, 200, 3, 40
+    x, a, b = (torch.randn(T, D, generator=g) for _ in range(3))
+    w, w2 = (1 + 0.2 * torch.randn(D, generator=g)).to(dtype), (1 + 0.2 * torch.randn(D, generator=g)).to(dtype)
+    tol = 1e-6 if dtype == torch.float32 else 8e-3
+    res = x.to(dev).clone()
+    h = blocks.add_norm(res, a.to(dev), b.to(dev), w.to(dev), 1e-5)
+    close(res, x.double() + a.double() + b.double(), 1e-6)
+    close(h, O.norm_plain(x.double() + a.double() + b.double(), w.double(), 1e-5), tol)
+    res = x.to(dev).clone()
+    assert blocks.add_norm(res, a.to(dev), None, None, 1e-5) is None
+    close(res, x.double() + a.double(), 1e-6)
+    want = 0.5 * (O.norm_plain(a.double(), w.double(), 1e-5) + O.norm_plain(b.double(), w2.double(), 1e-5))
+    close(blocks.norm_mix2(a.to(dev), w.to(dev), b.to(dev), w2.to(dev), 0.5, 1e-5), want, 1e-6)
+    o, gate, hw = torch.randn(T, H, dv, generator=g), torch.randn(T, H * dv, generator=g).to(dtype), (1 + 0.2 * torch.randn(dv, generator=g)).to(dtype)
+    want = O.norm_plain(o.double(), hw.double(), 1e-5).reshape(T, H * dv) * O.silu(gate.double())
+    close(blocks.head_norm_gate(o.to(dev), hw.to(dev), 1e-5, gate.to(dev), act=1), want, tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("experts,top,T", [(6, 2, 50), (4, 1, 7), (5, 5, 40), (16, 3, 300)])
+def test_sigmoid_router_and_input_weighted_experts_against_the_loop_over_tokens(dev, dtype, experts, top, T):
+    g = torch.Generator().manual_seed(experts)
+    D, ff = 48, 40
+    spec = {"router": {"experts": experts, "top": top}, "expert": {"ff": ff}}
+    w = {"router": torch.randn(experts, D, generator=g) * 0.3}
+    for e in range(experts):
+        w[f"e{e}.up"], w[f"e{e}.down"] = torch.randn(ff, D, generator=g) / D**0.5, torch.randn(D, ff, generator=g) / ff**0.5
+    w = {n: t.to(dtype) for n, t in w.items()}
+    h = torch.randn(T, D, generator=g).to(dtype)
+    idx, gate = blocks.moe_route(h.to(dev), w["router"].to(dev), None, top, blocks.SCORE_SIGMOID)
+    scores = torch.sigmoid(h.double() @ w["router"].double().T)
+    want_idx = torch.topk(scores, top, dim=-1).indices
+    if dtype == torch.float32:
+        assert torch.equal(idx.cpu().long().sort(-1).values, want_idx.sort(-1).values)
+    close(gate, torch.gather(scores, 1, idx.cpu().long()), 1e-6)
+    stack = lambda part: torch.stack([w[f"e{e}.{part}"] for e in range(experts)]).to(dev)
+    got = blocks.moe_experts(h.to(dev), idx, gate, None, stack("up"), stack("down"), blocks.ACT_RELU_SQUARED, None, scale_input=True)
+    if dtype == torch.float32:
+        close(got, O.expert_mixture(h.double(), {"x." + n: t for n, t in w.items()}, "x.", spec), 2e-6)
+    else:  # against the same choices (a close call may go the other way in bf16), weights on the rounded inputs
+        want = torch.zeros(T, D, dtype=torch.float64)
+        for t in range(T):
+            for j in range(top):
+                e = int(idx[t, j])
+                x = (gate[t, j].cpu().double() * h[t].double()).to(dtype).double()
+                want[t] += O.relu_squared(x @ w[f"e{e}.up"].double().T) @ w[f"e{e}.down"].double().T
+        close(got, want, 2e-2)
+
+
+# ---------------------------------------------------------------------------------------------- the model
+CONFIGS = {
+    # attention with its own cache, a parallel layer, a layer on the first layer's cache, another parallel one, no feed-forward at the end
+    "mixed": dict(pattern="APSPa", width=96, vocab=160, heads=4, kv_heads=2, dim=16, vdim=24, window=20, chunk=28, top=2, experts=6),
+    # sizes that coincide: one key/value head per query head, dim = vdim = the recurrent sizes, one expert per token, window = chunk = a page
+    "equal": dict(pattern="PAS", width=64, vocab=97, heads=2, kv_heads=2, dim=32, vdim=32, window=64, chunk=64, rec_heads=2, rec_dim=32, rec_vdim=32,
+                  top=1, experts=3, expert_ff=64, softcap=8.0),
+    # groups of three heads, odd sizes, a window of two tokens, chunks of five, a parallel layer first and one without feed-forward
+    "odd": dict(pattern="pAPS", width=72, vocab=131, heads=6, kv_heads=2, dim=24, vdim=40, window=2, chunk=5, rec_heads=3, rec_dim=12, rec_vdim=40,
+                tau=2.5, top=3, experts=5, expert_ff=24),
+}
+_models: dict = {}
+
+
+def model_and_oracle(dev, name, dtype, max_tokens=None, max_requests=None):
+    key = (name, dtype, max_tokens, max_requests)
+    if key not in _models:
+        config = bapovik_config(**CONFIGS[name])
+        tensors = synthetic_bapovik(config, seed=len(name))
+        model = model_class("Bapovik").from_checkpoint(config, tensors, dtype=dtype, device=dev, max_tokens=max_tokens, max_requests=max_requests)
+        _models[key] = (model, config, tensors)
+    return _models[key]
+
+
+def run_schedule(model, prompts, schedule):
+    """``schedule``: steps of [(request, count)]; every position's logits are collected.  Requests end (and give their
+    pages and state slot back) with their last token."""
+    caches, at, got = {}, {r: 0 for r in prompts}, {r: [] for r in prompts}
+    for step in schedule:
+        entries = []
+        for r, n in step:
+            caches.setdefault(r, model.create_kv_cache())
+            entries.append(RaggedEntry(prompts[r][at[r] : at[r] + n], caches[r], want=range(n)))
+        logits = model.forward_ragged(entries).cpu()
+        k = 0
+        for r, n in step:
+            got[r].append(logits[k : k + n])
+            k += n
+            at[r] += n
+            if at[r] == len(prompts[r]):
+                caches.pop(r)[0].release()
+    return {r: torch.cat(v) for r, v in got.items()}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_whole_prompt_matches_the_plain_model(dev, name, dtype):
+    model, config, tensors = model_and_oracle(dev, name, dtype)
+    prompt = ids_for(150, config["vocab"], 1)
+    want = O.forward(prompt, tensors, config)
+    got = run_schedule(model, {"a": prompt}, [[("a", len(prompt))]])["a"]
+    assert rows_match(got, want, dtype)
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_layers_one_by_one(dev, name):
+    """The residual stream after every layer (float32 mode), tapped from the model's own step."""
+    model, config, tensors = model_and_oracle(dev, name, torch.float32)
+    prompt = ids_for(70, config["vocab"], 2)
+    want = []
+    O.forward(prompt, tensors, config, trace=want)
+    cache = model.create_kv_cache()
+    model.stream_tap = []
+    try:
+        model.forward_ragged([RaggedEntry(prompt, cache)])
+        assert len(model.stream_tap) == len(want)
+        for x32, w in zip(model.stream_tap, want):
+            close(x32, w, 2e-5)
+    finally:
+        model.stream_tap = None
+        cache[0].release()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["mixed", "equal"])
+def test_prefill_then_token_by_token_decoding_across_windows_chunks_and_pages(dev, name, dtype):
+    model, config, tensors = model_and_oracle(dev, name, dtype)
+    prompt = ids_for(100 + 120, config["vocab"], 3)  # 120 decoded tokens: windows, chunk borders and two page borders pass by
+    want = O.forward(prompt, tensors, config)
+    replays = model.graph_replays
+    got = run_schedule(model, {"a": prompt}, [[("a", 100)]] + [[("a", 1)]] * 120)["a"]
+    assert rows_match(got, want, dtype)
+    assert model.graph_replays - replays >= 110  # single-token steps replay a captured graph from their third step on
+    model.use_decode_graph = False
+    try:
+        eager = run_schedule(model, {"a": prompt}, [[("a", 100)]] + [[("a", 1)]] * 120)["a"]
+    finally:
+        model.use_decode_graph = None
+    assert row_error(eager, got.double()) < 1e-6
+    alone = run_schedule(model, {"a": prompt[:40]}, [[("a", 1)]] * 40)["a"]  # the first tokens, one by one from nothing
+    assert rows_match(alone, want[:40], dtype)
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_portions_of_every_size_down_to_two(dev, name):
+    model, config, tensors = model_and_oracle(dev, name, torch.float32)
+    prompt = ids_for(203, config["vocab"], 4)
+    want = O.forward(prompt, tensors, config)
+    for sizes in ([2] * 20 + [3, 5, 64, 23, 2, 33, 31, 2], [63, 1, 64, 2, 62, 11], [7] * 29, [128, 75]):
+        assert sum(sizes) == len(prompt)
+        got = run_schedule(model, {"a": prompt}, [[("a", n)] for n in sizes])["a"]
+        assert row_error(got, want) < 5e-5, sizes
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_unequal_requests_in_one_batch_equal_each_alone_and_pages_and_slots_are_reused(dev, dtype):
+    model, config, tensors = model_and_oracle(dev, "mixed", dtype, max_tokens=5 * 64, max_requests=3)  # 5 pages, 3 state slots in all
+    prompts = {"a": ids_for(130, 160, 5), "b": ids_for(61, 160, 6), "c": ids_for(3, 160, 7), "d": ids_for(100, 160, 8), "e": ids_for(64, 160, 9)}
+    want = {r: O.forward(p, tensors, config) for r, p in prompts.items()}
+    schedule = [[("a", 60), ("b", 2)], [("a", 2), ("b", 58), ("c", 1)], [("a", 1), ("b", 1), ("c", 2)],   # b and c end: 2 pages and 2 slots back
+                [("a", 30), ("d", 50)], [("a", 37), ("d", 1)],                                           # a ends (3 pages), d in a reused page and slot
+                [("d", 49), ("e", 64)]]                                                                  # e fills a whole reused page
+    got = run_schedule(model, prompts, schedule)
+    pool, states = model.page_pool, model.state_pool
+    assert pool.reused_page_allocations >= 3 and pool.capacity == 5 and not pool.used_page_ids
+    assert states.reused_slot_allocations >= 2 and states.capacity == 3 and not states.used_slots
+    for r in prompts:
+        assert rows_match(got[r], want[r], dtype), r
+    if dtype == torch.float32:  # and the same as alone up to the summation order of the library products (which follows the row count)
+        alone = run_schedule(model, {"d": prompts["d"]}, [[("d", 50)], [("d", 1)], [("d", 49)]])["d"]
+        assert row_error(alone, got["d"].double()) < 2e-5
+    with pytest.raises(RuntimeError, match="exhausted"):
+        run_schedule(model, {"x": ids_for(330, 160, 1)}, [[("x", 330)]])
+    assert not pool.used_page_ids and not states.used_slots  # the refused step took nothing
+    live = [model.create_kv_cache() for _ in range(4)]
+    with pytest.raises(RuntimeError, match="state slots exhausted"):
+        model.forward_ragged([RaggedEntry([1, 2], c) for c in live])
+    assert not pool.used_page_ids and not states.used_slots
+
+
+def test_rectangular_call_scheduler_slots_and_offsets(dev):
+    model, config, tensors = model_and_oracle(dev, "mixed", torch.float32)
+    p0, p1 = ids_for(9, 160, 10), ids_for(5, 160, 11)
+    c0, c1 = model.create_kv_cache(), model.create_kv_cache()
+    l0 = model(torch.tensor([p0], dtype=torch.int32, device=dev), 0, c0)                 # all rows
+    l1 = model(torch.tensor([p1], dtype=torch.int32, device=dev), 0, c1, logits_to_keep=1)
+    assert l0.shape == (1, 9, 160) and l1.shape == (1, 1, 160)
+    assert row_error(l0[0], O.forward(p0, tensors, config)) < 2e-5
+    with pytest.raises(ValueError, match="offset"):
+        model(torch.tensor([[1]], dtype=torch.int32, device=dev), 3, c0)
+    tables = [BatchingKvCache(max_active_requests=3) for _ in range(model.num_hidden_layers)]
+    for t, a, b in zip(tables, c0, c1):
+        t.add_request(a, 2)
+        t.add_request(b, 0)
+    out = model(torch.tensor([[7], [0], [8]], dtype=torch.int32, device=dev), [5, 0, 9], tables, logits_to_keep=1)
+    assert out.shape == (3, 1, 160) and float(out[1].abs().max()) == 0.0               # the idle slot
+    assert row_error(out[2, 0], O.forward(p0 + [8], tensors, config)[-1]) < 2e-5
+    assert row_error(out[0, 0], O.forward(p1 + [7], tensors, config)[-1]) < 2e-5
+    for t in tables:
+        t.remove_request(0), t.remove_request(2)
+    assert not model.page_pool.used_page_ids and not model.state_pool.used_slots
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_greedy_generation_through_the_entry_points(dev, dtype, tmp_path):
+    """greedy_generate_ids and the continuous batcher (mixed steps, 2 slots, 5 requests, pages and state slots reused)
+    produce the plain model's greedy tokens; the checkpoint goes through a directory and load_model."""
+    config = bapovik_config(**CONFIGS["mixed"])
+    tensors = synthetic_bapovik(config, seed=21)
+    save_bapovik(config, tensors, tmp_path / "ckpt")
+    model = load_model(tmp_path / "ckpt", device=dev, dtype=dtype, max_tokens=6 * 64, max_requests=3)
+    prompts = [ids_for(n, 160, 30 + n) for n in (5, 70, 2, 33, 64)]
+    new = 40  # long enough for windows and a chunk border to pass over decoded tokens
+    want = [O.greedy(p, tensors, config, new) for p in prompts]
+    if dtype == torch.float32:
+        assert greedy_generate_ids(model, prompts[1], new, device=dev) == want[1]
+    batcher = ContinuousBatcher(model, None, prompts, max_seq_len=128, batch_size=2, prefill_step=16, verbose=False, device=dev,
+                                max_new_tokens=[new] * len(prompts))
+    results = dict(batcher.run())
+    got = [[int(t) for t in results[i].split()] for i in range(len(prompts))]
+    if dtype == torch.float32:
+        assert got == want
+    else:  # bf16: the same tokens until a near-tie, at least the first one of most requests
+        assert sum(g[:1] == w[:1] for g, w in zip(got, want)) >= len(prompts) - 1
+    assert batcher.mixed and batcher.mixed_steps > 0 and model.page_pool.reused_page_allocations > 0 and not model.page_pool.used_page_ids
+    assert model.state_pool.reused_slot_allocations > 0 and not model.state_pool.used_slots
+
+
+def test_trace_program_replays_steps_and_writes_logits(dev, tmp_path):
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    import numpy as np
+
+    config = bapovik_config(**CONFIGS["equal"])
+    tensors = synthetic_bapovik(config, seed=4)
+    save_bapovik(config, tensors, tmp_path / "ckpt")
+    a, b = ids_for(70, 97, 1), ids_for(9, 97, 2)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:66], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[66:], "want": [0, 3]}, {"id": "b", "tokens": b, "want": [8]}], "end": ["a", "b"]},
+             {"step": 2, "entries": [{"id": "c", "tokens": b, "want": [0]}], "end": ["c"]}]
+    root = Path(__file__).resolve().parent.parent
+    run = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(tmp_path / "ckpt"), "--dtype", "float32",
+                          "--out", str(tmp_path / "out"), "--max-tokens", "192"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                         capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, run.stderr[-2000:]
+    assert [l for l in run.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    assert not (tmp_path / "out" / "0.f32").exists()
+    got = torch.from_numpy(np.fromfile(tmp_path / "out" / "1.f32", dtype="<f4").reshape(3, 97))
+    wa, wb = O.forward(a, tensors, config), O.forward(b, tensors, config)
+    assert row_error(got, torch.stack([wa[66], wa[69], wb[8]])) < 2e-5
+    got = torch.from_numpy(np.fromfile(tmp_path / "out" / "2.f32", dtype="<f4").reshape(1, 97))
+    assert row_error(got, wb[:1]) < 2e-5
+
+
+def test_command_line_generates_and_batches(dev, tmp_path, capsys):
+    from tiny_llm_b200 import cli
+
+    config = bapovik_config(**CONFIGS["equal"])
+    tensors = synthetic_bapovik(config, seed=8)
+    save_bapovik(config, tensors, tmp_path / "ckpt")
+    prompt = ids_for(11, 97, 5)
+    want = O.greedy(prompt, tensors, config, 6)
+    assert cli.main(["generate", "--model", str(tmp_path / "ckpt"), "--dtype", "float32", "--prompt-ids", ",".join(map(str, prompt)),
+                     "--max-new-tokens", "6"]) == 0
+    assert [int(t) for t in capsys.readouterr().out.split()] == want
+    assert cli.main(["batch", "--model", str(tmp_path / "ckpt"), "--dtype", "float32", "--quiet", "--batch-size", "2", "--prefill-step", "4",
+                     "--max-new-tokens", "6", "--prompt-ids", ";".join(",".join(map(str, ids_for(n, 97, n))) for n in (11, 3, 7))]) == 0
+    out = capsys.readouterr().out
+    assert out.count("--- request") == 3
+    first = out.split("--- request 0\n")[1].split("\n")[0]
+    assert [int(t) for t in first.split()] == O.greedy(ids_for(11, 97, 11), tensors, config, 6)
+    assert cli.main(["generate", "--synthetic", "bapovik:APS", "--prompt-ids", "5,17,3", "--max-new-tokens", "4"]) == 0
+    assert len(capsys.readouterr().out.split()) == 4
