@@ -35,6 +35,8 @@ Numbers on the JSON line (decode):
   --workload voluzen  (not a BASELINE config) the Voluzen design - latent attention + mixture of experts, bf16 weights - at
             two sizes beside Qwen3 W4A16 of equal width / depth / heads / active feed-forward width: prefill and decode tok/s,
             and the design's kernels alone against the measured peaks; its own JSON line
+  --workload bapovik  (not a BASELINE config) the Bapovik design - windowed / chunked attention beside a recurrent mixer, experts,
+            bf16 weights - at two sizes beside Voluzen of equal size, and the design's kernels alone against the measured peaks
   cpu_baseline  the reference's CPU path (oracle.model: dense bf16 weights, readable operators) on the
             host cores, bounded sample
 """
@@ -1015,13 +1017,185 @@ def run_voluzen(args) -> None:
                       "steps": steps, "warmup": max(args.warmup, 3), "peaks": measured_peaks(), "clocks": clocks, "sizes": results}), flush=True)
 
 
+# ------------------------------------------------------------------ workload: bapovik (windowed / chunked attention + recurrent mixer + experts, beside Voluzen of equal size)
+BAPOVIK_SIZES = {
+    # a few layers at sizes that resemble real models of this kind.  The Voluzen arm (the framework's closest model: bf16 weights,
+    # paged attention, experts, the same ragged step) has the same width, depth, head count, query/key and value sizes, window,
+    # experts and top; its gated experts have 2/3 of the width, so that an expert has the same number of weights.
+    "w1024": dict(width=1024, vocab=32768, pattern="APSP", heads=8, kv_heads=2, dim=96, vdim=64, window=512, chunk=512, softcap=30.0,
+                  rec_heads=8, rec_dim=64, rec_vdim=128, tau=16.0, experts=16, top=2, expert_ff=768),
+    "w2048": dict(width=2048, vocab=32768, pattern="APSP", heads=16, kv_heads=4, dim=192, vdim=128, window=1024, chunk=1024, softcap=30.0,
+                  rec_heads=16, rec_dim=64, rec_vdim=128, tau=16.0, experts=64, top=6, expert_ff=2112),
+}
+
+
+def _bapovik_kernels(cfg: dict, device, prompt: int, batch: int, context: int) -> dict:
+    """The design's own kernels alone at this size, CUDA-event timed after warm-up, each against the roofline of its kind
+    (measured cuBLAS bf16 burst for contractions, measured copy bandwidth for streaming kernels); between repetitions a
+    256 MB buffer is rewritten to flush L2."""
+    from extensions_b200.tiny_llm_ext_b200 import blocks
+
+    peaks = measured_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    bf = torch.bfloat16
+
+    def timed(fn, reps=5):
+        for _ in range(3):
+            fn()
+        best = []
+        for _ in range(reps):
+            flush.fill_(1)
+            best.append(cuda_time_ms(fn))
+        return statistics.median(best)
+
+    H, G, dk, dv, D, window = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg["vdim"], cfg["width"], cfg["window"]
+    page, out = 64, {}
+    kernel, tile = blocks.paged_attention_kernel(bf, H, G, dk, dv, page)
+
+    def attention(tokens_per_seq, seqs, ctx):
+        pages_per = -(-ctx // page)
+        slab = torch.randn((seqs * pages_per, page, G * (dk + dv)), dtype=torch.float32, device=device).to(bf)
+        table = torch.arange(seqs * pages_per, dtype=torch.int32, device=device).view(seqs, pages_per)
+        T = tokens_per_seq * seqs
+        pos = torch.cat([torch.arange(ctx - tokens_per_seq, ctx, dtype=torch.int32) for _ in range(seqs)]).to(device)
+        tiles = torch.tensor([(s * tokens_per_seq + f, min(tile, tokens_per_seq - f), s) for s in range(seqs) for f in range(0, tokens_per_seq, tile)],
+                             dtype=torch.int32, device=device)
+        q = torch.randn((T, H, dk), dtype=torch.float32, device=device).to(bf)
+        gate = torch.randn((T, H), dtype=torch.float32, device=device).to(bf)
+        o = torch.empty((T, H, dv), dtype=bf, device=device)
+        return timed(lambda: blocks.paged_attention(q, slab, table, tiles, pos, kv_heads=G, dv=dv, mask=blocks.MASK_WINDOW, mask_size=window, scale=0.05,
+                                                    softcap=30.0, sink=True, gate=gate, out=o, kernel=kernel))
+
+    ms = attention(prompt, 1, prompt)
+    seen = sum(min(i + 1, window) for i in range(prompt))
+    flops = 2.0 * H * (dk + dv) * seen
+    out["paged_attention_prefill"] = {"kernel": kernel, "tokens": prompt, "window": window, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
+                                      "of_measured_bf16_burst": round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)}
+    ms = attention(1, batch, context)
+    cache_bytes = batch * min(context, window) * G * (dk + dv) * 2
+    out["paged_attention_decode"] = {"kernel": kernel, "batch": batch, "context": context, "window": window, "ms": round(ms, 4),
+                                     "gbs": round(cache_bytes / ms / 1e6, 1), "of_measured_hbm": round(cache_bytes / ms / 1e6 / peaks["hbm_gbs"], 4)}
+    RH, rk, rv, tau = cfg["rec_heads"], cfg["rec_dim"], cfg["rec_vdim"], cfg["tau"]
+
+    def scan(tokens_per_seq, seqs, start):
+        T = tokens_per_seq * seqs
+        q, k = (torch.randn((T, RH, rk), device=device).to(bf) for _ in range(2))
+        v = torch.randn((T, RH, rv), device=device).to(bf)
+        z = torch.randn((T, RH * rk), device=device)
+        info = torch.tensor([(s * tokens_per_seq, tokens_per_seq, start, s) for s in range(seqs)], dtype=torch.int32, device=device)
+        state = torch.zeros((seqs, RH, rk, rv), device=device)
+        return timed(lambda: blocks.decay_scan(q, k, v, z, None, tau=tau, q_scale=rk ** -0.5, seq_info=info, state=state))
+
+    ms = scan(prompt, 1, 0)
+    nbytes = prompt * RH * (2 * rk * 2 + rv * 2 + rk * 4 + rv * 4)
+    out["decay_scan_prefill"] = {"tokens": prompt, "ms": round(ms, 4), "us_per_token": round(ms * 1e3 / prompt, 3), "gflops": round(4.0 * prompt * RH * rk * rv / ms / 1e6, 1),
+                                 "gbs": round(nbytes / ms / 1e6, 1), "of_measured_hbm": round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 4),
+                                 "note": "one sequence is walked token by token: the bound is the chain of dependent steps, not bytes"}
+    ms = scan(1, batch, context)
+    nbytes = batch * RH * rk * rv * 4 * 2
+    out["decay_scan_decode"] = {"batch": batch, "ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1), "of_measured_hbm": round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 4)}
+    E, top, ff = cfg["experts"], cfg["top"], cfg["expert_ff"]
+    g = torch.Generator(device="cpu").manual_seed(0)
+    h = torch.randn((prompt, D), generator=g).to(bf).to(device)
+    wu = (torch.randn((E, ff, D), device=device) / D**0.5).to(bf)
+    wd = (torch.randn((E, D, ff), device=device) / ff**0.5).to(bf)
+    router_w = torch.randn((E, D), device=device).to(bf)
+    idx, gate = blocks.moe_route(h, router_w, None, top, blocks.SCORE_SIGMOID)
+    ms = timed(lambda: blocks.moe_experts(h, idx, gate, None, wu, wd, blocks.ACT_RELU_SQUARED, None, scale_input=True))
+    flops = 2.0 * 2 * prompt * top * ff * D
+    out["moe_experts_prefill"] = {"tokens": prompt, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
+                                  "of_measured_bf16_burst": round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)}
+    hb = h[:batch].contiguous()
+    idx, gate = blocks.moe_route(hb, router_w, None, top, blocks.SCORE_SIGMOID)
+    ms = timed(lambda: blocks.moe_experts(hb, idx, gate, None, wu, wd, blocks.ACT_RELU_SQUARED, None, scale_input=True))
+    touched = min(E, batch * top) * 2 * ff * D * 2
+    out["moe_experts_decode"] = {"batch": batch, "ms": round(ms, 4), "gbs_upper": round(touched / ms / 1e6, 1),
+                                 "of_measured_hbm_upper": round(touched / ms / 1e6 / peaks["hbm_gbs"], 4)}
+    rows = 65536  # > L2 in fp32
+    a, b, res = (torch.randn((rows, D), device=device) for _ in range(3))
+    w = torch.ones(D, device=device).to(bf)
+    ms = timed(lambda: blocks.add_norm(res, a, b, w, 1e-5))
+    nbytes = rows * D * (4 + 4 + 4 + 4 + 2)
+    out["add_norm"] = {"rows": rows, "ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1), "of_measured_hbm": round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 4)}
+    return out
+
+
+def run_bapovik(args) -> None:
+    """Prefill and decode throughput of the Bapovik design at BAPOVIK_SIZES beside Voluzen (the framework's closest model)
+    of equal size, through the same ragged step; and the design's kernels against their rooflines.  One JSON line; random
+    weights, random prompts."""
+    from tiny_llm_b200.batch import greedy_tokens
+    from tiny_llm_b200.models import model_class
+    from tiny_llm_b200.ragged import RaggedEntry
+    from tiny_llm_b200.synthetic import bapovik_config, synthetic_bapovik, synthetic_voluzen, voluzen_config
+
+    device = torch.device("cuda:0")
+    prompt, batch, context, steps = args.prompt_len or 2048, 16, 1024, max(args.steps or 16, 4)
+    sampler = ClockSampler(0)
+    sampler.start()
+
+    def measure(model, vocab):
+        ids = synthetic_prompt(1, prompt, vocab)
+
+        def prefill_once():
+            cache = model.create_kv_cache()
+            model.forward_ragged([RaggedEntry(ids, cache)])
+            cache[0].release()
+
+        for _ in range(max(args.warmup, 3)):
+            prefill_once()
+        pre_ms = statistics.median(cuda_time_ms(prefill_once) for _ in range(5))
+        caches = [model.create_kv_cache() for _ in range(batch)]
+        for b, cache in enumerate(caches):
+            model.forward_ragged([RaggedEntry(synthetic_prompt(10 + b, context, vocab), cache)])
+        tokens = [1] * batch
+
+        def decode_step():
+            nonlocal tokens
+            logits = model.forward_ragged([RaggedEntry([t], c) for t, c in zip(tokens, caches)])
+            tokens = greedy_tokens(logits).tolist()  # the device -> host read a serving step makes
+
+        for _ in range(max(args.warmup, 3)):
+            decode_step()
+        torch.cuda.synchronize()
+        dec_ms = cuda_time_ms(lambda: [decode_step() for _ in range(steps)]) / steps
+        for cache in caches:
+            cache[0].release()
+        return {"prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(prompt / pre_ms * 1e3, 1), "decode_ms_per_step": round(dec_ms, 3),
+                "decode_tok_s": round(batch / dec_ms * 1e3, 1)}
+
+    results = []
+    for name, size in BAPOVIK_SIZES.items():
+        config = bapovik_config(**size)
+        model = model_class("Bapovik").from_checkpoint(config, synthetic_bapovik(config, seed=0), device=device, dtype=torch.bfloat16)
+        entry = {"size": name, "config": dict(size), "prompt_tokens": prompt, "decode_batch": batch, "decode_context": context,
+                 "bapovik": measure(model, size["vocab"])}
+        entry["kernels"] = _bapovik_kernels(size, device, prompt, batch, context)
+        del model
+        torch.cuda.empty_cache()
+        rot = size["dim"] // 3
+        vsize = dict(width=size["width"], vocab=size["vocab"], pattern="wMSM", heads=size["heads"], dim=size["dim"] - rot, rot_dim=rot, vdim=size["vdim"],
+                     kv_rank=min(512, size["kv_heads"] * (size["dim"] + size["vdim"]) // 2), window=size["window"], experts=size["experts"], top=size["top"],
+                     expert_ff=size["expert_ff"] * 2 // 3, shared_ff=0)
+        vconfig = voluzen_config(**vsize)
+        other = model_class("Voluzen").from_checkpoint(vconfig, synthetic_voluzen(vconfig, seed=0), device=device, dtype=torch.bfloat16)
+        entry["voluzen_equal_size"] = dict(measure(other, size["vocab"]), config=vsize)
+        del other
+        torch.cuda.empty_cache()
+        results.append(entry)
+    clocks = sampler.stop()
+    print(json.dumps({"workload": "bapovik", "metric": "Bapovik prefill / decode tok/s beside Voluzen of equal size", "unit": UNIT, "n_gpus": 1,
+                      "dtype": "bf16 (unquantised weights in both)", "data": "synthetic (random weights, random prompts)",
+                      "steps": steps, "warmup": max(args.warmup, 3), "peaks": measured_peaks(), "clocks": clocks, "sizes": results}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(METRICS) + ["voluzen"], default="decode")
+    ap.add_argument("--workload", choices=sorted(METRICS) + ["voluzen", "bapovik"], default="decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the sweeps / secondary measurements under `extra`")
     ap.add_argument("--requests", type=int, default=0, help="serve/serve8k: total requests over all ranks")
@@ -1033,6 +1207,8 @@ def main() -> None:
         args.steps = {"decode": 128, "prefill": 8}.get(args.workload, 0)
     if args.workload == "voluzen":
         run_voluzen(args)
+    elif args.workload == "bapovik":
+        run_bapovik(args)
     elif args.impl == "reference":
         run_reference(args)
     elif args.workload == "decode":

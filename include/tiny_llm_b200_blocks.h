@@ -106,6 +106,15 @@ int tlb_paged_attention(const void *q, long long q_token, long long q_head, cons
                         int heads, int kv_heads, const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles,
                         const int32_t *tok_pos, int mask, int mask_size, float scale, float softcap, int sink, const void *gate,
                         long long g_token, void *out, long long o_token, long long o_head, int dtype, void *stream);
+/* The same on the tensor cores, for the bf16 cache: 32 query rows per CTA = tile_tokens consecutive tokens x the query heads
+ * of one key/value head (up to 32), tile_tokens = tlb_paged_attention_mma_tile_tokens(heads, kv_heads) the most tokens a tile
+ * may hold.  Needs dk, dv multiples of 8 up to 256 and page_size % 32 == 0 (tlb_paged_attention_mma_supported). */
+int tlb_paged_attention_mma_tile_tokens(int heads, int kv_heads);
+int tlb_paged_attention_mma_supported(int dk, int dv, int kv_heads, int page_size);
+int tlb_paged_attention_mma(const void *q, long long q_token, long long q_head, const void *slab, int num_pages, int page_size, int dk, int dv,
+                            int heads, int kv_heads, const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles,
+                            const int32_t *tok_pos, int mask, int mask_size, float scale, float softcap, int sink, const void *gate,
+                            long long g_token, void *out, long long o_token, long long o_head, void *stream);
 /* Before that attention: per-head RMS norm (plain weight [dk]) of the queries in place (q_norm != NULL) and of the keys
  * (k_norm != NULL), and the token's keys and values stored at its slot of the cache (k != NULL). */
 int tlb_kv_prepare(void *q, long long q_token, long long q_head, int heads, const void *q_norm, const void *k, long long k_token, long long k_head,

@@ -105,31 +105,65 @@ def test_paged_attention_against_plain_attention(dev, dtype, heads, kv_heads, dk
     assert torch.equal(part, got[S - 9 :])
 
 
+@pytest.mark.parametrize("heads,kv_heads,dk,dv", [(4, 4, 16, 16), (6, 2, 24, 40), (8, 1, 8, 72), (2, 2, 64, 32), (64, 1, 16, 24), (3, 1, 200, 256)])
+@pytest.mark.parametrize("kind,size,softcap,sink", [("causal", 0, 0.0, False), ("window", 37, 0.0, False), ("chunk", 50, 4.0, True), ("window", 1, 2.0, True)])
+def test_tensor_core_attention_against_plain_attention_and_the_general_kernel(dev, heads, kv_heads, dk, dv, kind, size, softcap, sink):
+    g = torch.Generator().manual_seed(heads * dk + size)
+    S, bf = 150, torch.bfloat16
+    q, k, v = torch.randn(S, heads, dk, generator=g).to(bf), torch.randn(S, kv_heads, dk, generator=g).to(bf), torch.randn(S, kv_heads, dv, generator=g).to(bf)
+    gate = torch.randn(S, heads, generator=g).to(bf)
+    scale = dk ** -0.5
+    want = O.masked_attention(q.double(), k.double(), v.double(), scale=scale, kind=kind, size=size, softcap=softcap or None, sink=sink)
+    want = want * torch.sigmoid(gate.double())[:, :, None]
+    cache = Paged(dev, bf, k, v)
+    name, tile = blocks.paged_attention_kernel(bf, heads, kv_heads, dk, dv, 32)
+    assert name == "mma" and tile == max(1, 32 // (heads // kv_heads))
+    args = dict(kv_heads=kv_heads, dv=dv, mask=MASK[kind], mask_size=size, scale=scale, softcap=softcap, sink=sink)
+    tiles, pos = cache.tiles(dev, 0, S, tile)
+    got = blocks.paged_attention(q.to(dev), cache.slab, cache.table, tiles, pos, gate=gate.to(dev), kernel="mma", **args)
+    close(got, want, 2e-2)
+    tiles_g, _ = cache.tiles(dev, 0, S, blocks.paged_attention_tile_tokens(heads, kv_heads))
+    general = blocks.paged_attention(q.to(dev), cache.slab, cache.table, tiles_g, pos, gate=gate.to(dev), **args)
+    close(got, general.double().cpu(), 2e-2)
+    # the last 9 tokens alone, and the very last one as a decoded token: the same rows, bit for bit
+    tiles, pos = cache.tiles(dev, S - 9, 9, tile)
+    part = blocks.paged_attention(q[S - 9 :].to(dev), cache.slab, cache.table, tiles, pos, gate=gate[S - 9 :].to(dev), kernel="mma", **args)
+    assert torch.equal(part, got[S - 9 :])
+    tiles, pos = cache.tiles(dev, S - 1, 1, tile)
+    one = blocks.paged_attention(q[S - 1 :].to(dev), cache.slab, cache.table, tiles, pos, gate=gate[S - 1 :].to(dev), kernel="mma", **args)
+    assert torch.equal(one, got[S - 1 :])
+    assert blocks.paged_attention_kernel(bf, 4, 2, 12, 16, 32)[0] == "general" and blocks.paged_attention_kernel(torch.float32, 4, 2, 16, 16, 32)[0] == "general"
+
+
+@pytest.mark.parametrize("kernel", ["general", "mma"])
 @pytest.mark.parametrize("kind,size", [("window", 70), ("window", 64), ("chunk", 70), ("chunk", 64), ("causal", 0)])
-def test_one_key_that_matters_far_away_at_page_borders_and_mask_edges(dev, kind, size):
+def test_one_key_that_matters_far_away_at_page_borders_and_mask_edges(dev, kind, size, kernel):
     """All keys are noise but one, which the probing query scores far above the rest: the output is that key's value
     exactly when the mask lets the query see it.  Prompt rows and single decoded tokens, page size 32."""
     g = torch.Generator().manual_seed(size)
     S, dk, dv = 400, 16, 8
+    dtype = torch.float32 if kernel == "general" else torch.bfloat16
+    tile = blocks.paged_attention_kernel(dtype, 2, 1, dk, dv, 32)[1]
     for target in (0, 31, 32, 63, 64, 200, 329, 330, 331, 398, 399):
         k, v = 0.05 * torch.randn(S, 1, dk, generator=g), torch.randn(S, 1, dv, generator=g)
         k[target, 0, 3] = 40.0
         v[target] = 5.0
         q = torch.zeros(S, 2, dk)
         q[:, :, 3] = 1.0
-        cache = Paged(dev, torch.float32, k, v, seed=target)
-        tile = blocks.paged_attention_tile_tokens(2, 1)
+        cache = Paged(dev, dtype, k, v, seed=target)
+        q = q.to(dtype)
         tiles, pos = cache.tiles(dev, 0, S, tile)
-        whole = blocks.paged_attention(q.to(dev), cache.slab, cache.table, tiles, pos, kv_heads=1, dv=dv, mask=MASK[kind], mask_size=size, scale=1.0).cpu()
+        whole = blocks.paged_attention(q.to(dev), cache.slab, cache.table, tiles, pos, kv_heads=1, dv=dv, mask=MASK[kind], mask_size=size, scale=1.0,
+                                       kernel=kernel).float().cpu()
         for i in sorted({target, target + 1, target + size - 2, target + size - 1, target + size, target + size + 1, (target // max(size, 1) + 1) * max(size, 1) - 1,
                          (target // max(size, 1) + 1) * max(size, 1), S - 1}):
             if not 0 <= i < S:
                 continue
             sees = O.visible(i, target, kind, size)
-            assert (whole[i, 0] - 5.0).abs().max().item() < 1e-3 if sees else (whole[i, 0] - 5.0).abs().min().item() > 1.0, (target, i)
+            assert (whole[i, 0] - 5.0).abs().max().item() < 2e-2 if sees else (whole[i, 0] - 5.0).abs().min().item() > 1.0, (target, i)
             tiles1, pos1 = cache.tiles(dev, i, 1, tile)  # the same position as a single decoded token
             one = blocks.paged_attention(q[i : i + 1].to(dev), cache.slab, cache.table, tiles1, pos1, kv_heads=1, dv=dv, mask=MASK[kind], mask_size=size,
-                                         scale=1.0).cpu()
+                                         scale=1.0, kernel=kernel).float().cpu()
             assert torch.equal(one[0], whole[i])
 
 
@@ -158,9 +192,9 @@ def test_keys_and_values_land_on_their_slots_with_per_head_norms(dev, dtype, nor
     q, k, v = (torch.randn(T, n, generator=g).to(dtype) for n in (H * dk, G * dk, G * dv))
     qn, kn = (1 + 0.3 * torch.randn(dk, generator=g)).to(dtype), (1 + 0.3 * torch.randn(dk, generator=g)).to(dtype)
     slab = torch.zeros((4, page, G * (dk + dv)), dtype=dtype, device=dev)
-    pos = torch.tensor([30, 31, 32, 33, 34, 0, 1, 63, 64], dtype=torch.int32)   # sequence 0: positions 30..34, sequence 1: 0, 1, sequence 2: 63, 64
+    pos = torch.tensor([30, 31, 32, 33, 34, 0, 1, 31, 32], dtype=torch.int32)   # sequence 0: positions 30..34, sequence 1: 0, 1, sequence 2: 31, 32
     seq = torch.tensor([0, 0, 0, 0, 0, 1, 1, 2, 2], dtype=torch.int32)
-    table = torch.tensor([[3, 1, -1], [0, -1, -1], [9, 2, 0]], dtype=torch.int32)  # page 9 does not exist: position 63 of sequence 2 is dropped
+    table = torch.tensor([[3, 1, -1], [0, -1, -1], [9, 2, -1]], dtype=torch.int32)  # page 9 does not exist: position 31 of sequence 2 is dropped
     qd = q.to(dev).clone()
     blocks.kv_prepare(qd.view(T, H, dk), k.to(dev).view(T, G, dk), v.to(dev).view(T, G, dv), q_norm=qn.to(dev) if normed else None,
                       k_norm=kn.to(dev) if normed else None, eps=1e-5, tok_pos=pos.to(dev), tok_seq=seq.to(dev), block_table=table.to(dev), slab=slab)
@@ -168,9 +202,10 @@ def test_keys_and_values_land_on_their_slots_with_per_head_norms(dev, dtype, nor
     want_q = O.norm_plain(q.double().view(T, H, dk), qn.double(), 1e-5) if normed else q.double().view(T, H, dk)
     close(qd.view(T, H, dk), want_q, tol)
     want_k = O.norm_plain(k.double().view(T, G, dk), kn.double(), 1e-5) if normed else k.double().view(T, G, dk)
-    for t, (page_id, slot) in enumerate([(3, 30), (3, 31), (1, 0), (1, 1), (1, 2), (0, 0), (0, 1), None, (2, 0)]):
-        if page_id is None:
+    for t, where in enumerate([(3, 30), (3, 31), (1, 0), (1, 1), (1, 2), (0, 0), (0, 1), None, (2, 0)]):
+        if where is None:
             continue
+        page_id, slot = where
         row = slab[page_id, slot].cpu()
         close(row[: G * dk].view(G, dk), want_k[t], tol)
         assert torch.equal(row[G * dk :], v[t])

@@ -47,6 +47,7 @@ BLOCKS_SOURCES = [
     "blocks/blocks_latent_attention_mma.cu",
     "blocks/blocks_moe.cu",
     "blocks/blocks_paged_attention.cu",
+    "blocks/blocks_paged_attention_mma.cu",
     "blocks/blocks_linear_attention.cu",
 ]
 

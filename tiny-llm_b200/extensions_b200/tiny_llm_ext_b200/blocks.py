@@ -43,6 +43,9 @@ _SIGNATURES = {
     "tlb_norm_mix2": (_I, [_VP, _VP, _VP, _VP, _F, _F, _VP, _I, _I, _I, _VP]),
     "tlb_paged_attention_tile_tokens": (_I, [_I, _I]),
     "tlb_paged_attention": (_I, [_VP, _LL, _LL, _VP, _I, _I, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _F, _I, _VP, _LL, _VP, _LL, _LL, _I, _VP]),
+    "tlb_paged_attention_mma_tile_tokens": (_I, [_I, _I]),
+    "tlb_paged_attention_mma_supported": (_I, [_I, _I, _I, _I]),
+    "tlb_paged_attention_mma": (_I, [_VP, _LL, _LL, _VP, _I, _I, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _F, _I, _VP, _LL, _VP, _LL, _LL, _VP]),
     "tlb_kv_prepare": (_I, [_VP, _LL, _LL, _I, _VP, _VP, _LL, _LL, _VP, _LL, _LL, _I, _I, _I, _VP, _F, _VP, _VP, _VP, _I, _I, _I, _VP, _I, _I, _VP]),
     "tlb_decay_scan": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _VP, _F, _F, _I, _I, _I, _VP, _I, _VP, _LL, _I, _VP, _I, _VP]),
     "tlb_head_norm_gate": (_I, [_VP, _VP, _F, _VP, _LL, _I, _VP, _I, _I, _I, _I, _VP]),
@@ -372,12 +375,23 @@ def norm_mix2(a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: torch.Tens
     return y
 
 
-def paged_attention_tile_tokens(heads: int, kv_heads: int) -> int:
-    """The most tokens an entry of ``tiles`` may hold for ``paged_attention`` with these head counts."""
-    n = int(library().tlb_paged_attention_tile_tokens(heads, kv_heads))
+def paged_attention_kernel(dtype, heads: int, kv_heads: int, dk: int, dv: int, page_size: int) -> tuple[str, int]:
+    """Which grouped-query attention kernel serves these sizes, and the most tokens one entry of its ``tiles`` may hold:
+    ``("mma", 32 // group)`` for a bf16 cache the tensor-core kernel can take (32 query rows per CTA), else
+    ``("general", 16 // min(group, 4))`` (fp32 cache, odd head sizes; TL_PAGED_MMA=0 forces it)."""
+    lib = library()
+    if dtype == torch.bfloat16 and os.environ.get("TL_PAGED_MMA", "1") != "0" and lib.tlb_paged_attention_mma_supported(dk, dv, kv_heads, page_size):
+        name, n = "mma", int(lib.tlb_paged_attention_mma_tile_tokens(heads, kv_heads))
+    else:
+        name, n = "general", int(lib.tlb_paged_attention_tile_tokens(heads, kv_heads))
     if n <= 0:
         raise RuntimeError(f"paged_attention: {heads} heads do not divide into {kv_heads} key/value heads")
-    return n
+    return name, n
+
+
+def paged_attention_tile_tokens(heads: int, kv_heads: int) -> int:
+    """The most tokens an entry of ``tiles`` may hold for the general ``paged_attention`` kernel with these head counts."""
+    return paged_attention_kernel(torch.float32, heads, kv_heads, 1, 1, 32)[1]
 
 
 def kv_prepare(q, k, v, *, q_norm=None, k_norm=None, eps: float = 0.0, tok_pos=None, tok_seq=None, block_table=None, slab=None):
@@ -406,9 +420,10 @@ def kv_prepare(q, k, v, *, q_norm=None, k_norm=None, eps: float = 0.0, tok_pos=N
 
 
 def paged_attention(q, slab, block_table, tiles, tok_pos, *, kv_heads: int, dv: int, mask: int, mask_size: int, scale: float, softcap: float = 0.0,
-                    sink: bool = False, gate=None, out=None):
+                    sink: bool = False, gate=None, out=None, kernel: str = "general"):
     """``q [T, H, dk]`` (a view with unit inner stride) against ``slab [P, page, kv_heads * (dk + dv)]`` -> ``out [T, H, dv]``
-    (contiguous, the query's dtype).  ``gate [T, H]`` (a view with unit inner stride): logits of a sigmoid output gate."""
+    (contiguous, the query's dtype).  ``gate [T, H]`` (a view with unit inner stride): logits of a sigmoid output gate.
+    ``kernel`` and the tile size of ``tiles`` come from ``paged_attention_kernel``."""
     _gpu("paged_attention", q, slab, block_table, tiles, tok_pos, gate, out)
     _contig("paged_attention", slab, block_table, tiles, tok_pos)
     T, H, dk = q.shape
@@ -419,6 +434,16 @@ def paged_attention(q, slab, block_table, tiles, tok_pos, *, kv_heads: int, dv: 
         raise RuntimeError("paged_attention: gate must be [T, H] of the query's dtype")
     if out is None:
         out = torch.empty((T, H, dv), dtype=q.dtype, device=q.device)
+    if kernel == "mma":
+        if slab.dtype != torch.bfloat16:
+            raise RuntimeError("paged_attention: the tensor-core kernel takes a bfloat16 cache")
+        _check(library().tlb_paged_attention_mma(_ptr(q), q.stride(0), q.stride(1), _ptr(slab), P, page_size, dk, dv, H, kv_heads, _ptr(block_table),
+                                                 block_table.shape[1], _ptr(tiles), tiles.shape[0], _ptr(tok_pos), int(mask), int(mask_size),
+                                                 float(scale), float(softcap or 0.0), int(bool(sink)), _ptr(gate),
+                                                 gate.stride(0) if gate is not None else 0, _ptr(out), out.stride(0), out.stride(1), _stream(q)))
+        return out
+    if kernel != "general":
+        raise RuntimeError(f"paged_attention: unknown kernel {kernel!r}")
     _check(library().tlb_paged_attention(_ptr(q), q.stride(0), q.stride(1), _ptr(slab), P, page_size, dk, dv, H, kv_heads, _ptr(block_table),
                                          block_table.shape[1], _ptr(tiles), tiles.shape[0], _ptr(tok_pos), int(mask), int(mask_size), float(scale),
                                          float(softcap or 0.0), int(bool(sink)), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out),

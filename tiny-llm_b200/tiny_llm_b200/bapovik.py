@@ -96,7 +96,7 @@ class BapovikModel(RaggedDecoderModel):
                 heads=a["heads"], kv_heads=a["kv_heads"], dim=a["dim"], vdim=a["vdim"], scale=a["scale"],
                 mask="chunk" if kind == "parallel" else "window", mask_size=a["mask"]["size"], w_o=take(p + "o"), softcap=a.get("softcap"),
                 sink=kind == "parallel", q_norm=take(p + "q.norm") if normed else None, k_norm=take(p + "k.norm") if normed and own else None,
-                eps=self.eps, caches=own)
+                eps=self.eps, caches=own, page_size=page_size)
             parts = [(p + "q", take(p + "q"), take(p + "q.b"))]
             if own:
                 parts += [(p + "k", take(p + "k"), take(p + "k.b")), (p + "v", take(p + "v"), take(p + "v.b"))]

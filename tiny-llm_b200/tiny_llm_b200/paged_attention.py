@@ -46,7 +46,7 @@ class FusedProjection:
 
 class PagedGroupedAttention:
     def __init__(self, *, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, mask: str, mask_size: int, w_o, softcap: float | None = None,
-                 sink: bool = False, q_norm=None, k_norm=None, eps: float = 1e-6, caches: bool = True):
+                 sink: bool = False, q_norm=None, k_norm=None, eps: float = 1e-6, caches: bool = True, page_size: int = 64):
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads do not divide into {kv_heads} key/value heads")
         if mask not in MASKS or (mask != "causal" and int(mask_size) <= 0):
@@ -59,16 +59,14 @@ class PagedGroupedAttention:
         self.q_norm = None if q_norm is None else q_norm.contiguous()
         self.k_norm = None if k_norm is None else k_norm.contiguous()
         self.w_o = w_o.contiguous()
+        from extensions_b200.tiny_llm_ext_b200 import blocks
+
+        # the kernel (tensor cores for a bf16 cache of fitting sizes, else the general one) and its work-list granularity
+        self.kernel, self.tile_tokens = blocks.paged_attention_kernel(self.w_o.dtype, self.heads, self.kv_heads, self.dim, self.vdim, int(page_size))
 
     @property
     def cache_width(self) -> int:
         return self.kv_heads * (self.dim + self.vdim)
-
-    @property
-    def tile_tokens(self) -> int:
-        from extensions_b200.tiny_llm_ext_b200 import blocks
-
-        return blocks.paged_attention_tile_tokens(self.heads, self.kv_heads)
 
     def __call__(self, q, k, v, gate, plan, slab: torch.Tensor) -> torch.Tensor:
         from extensions_b200.tiny_llm_ext_b200 import blocks
@@ -81,5 +79,5 @@ class PagedGroupedAttention:
         elif self.q_norm is not None:
             blocks.kv_prepare(q3, None, None, q_norm=self.q_norm, eps=self.eps)
         o = blocks.paged_attention(q3, slab, plan.block_table, plan.tiles_for(self.tile_tokens), plan.tok_pos, kv_heads=G, dv=self.vdim, mask=self.mask,
-                                   mask_size=self.mask_size, scale=self.scale, softcap=self.softcap, sink=self.sink, gate=gate)
+                                   mask_size=self.mask_size, scale=self.scale, softcap=self.softcap, sink=self.sink, gate=gate, kernel=self.kernel)
         return linear_wide(o.view(T, H * self.vdim), self.w_o)  # fp32: a norm or the residual sum reads it unrounded
