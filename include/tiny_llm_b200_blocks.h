@@ -127,11 +127,17 @@ int tlb_kv_prepare(void *q, long long q_token, long long q_head, int heads, cons
  * seq_info [num_seqs, 4] int32: first flat token, token count, position of the first token, state slot.  A sequence at
  * position 0 starts from zero; the slot (state + slot * slot_stride floats, [heads, dk, dv]) is written after the last
  * token.  q, k [T, heads, dk], v [T, heads, dv] views (strides in elements), z [T, heads * dk] fp32 rows z_token apart,
- * z_bias `dtype` or NULL, out [T, heads, dv] fp32 contiguous.  dk <= 128. */
+ * z_bias `dtype` or NULL, out [T, heads, dv] fp32 contiguous.  dk <= 128.
+ * max_tokens_per_seq = the largest token count in seq_info (known to the host).  Up to TLB_DECAY_SCAN_SEGMENT tokens a
+ * sequence is walked in one go.  Longer portions are cut at the multiples of the segment length in absolute positions and
+ * run in three launches (every segment's local end state and decay product from a zero state; the segments' start
+ * states by walking those in order; outputs per segment), which needs tlb_decay_scan_workspace(...) bytes. */
+#define TLB_DECAY_SCAN_SEGMENT 64
+size_t tlb_decay_scan_workspace(int num_seqs, int max_tokens_per_seq, int heads, int dk, int dv);
 int tlb_decay_scan(const void *q, long long q_token, long long q_head, const void *k, long long k_token, long long k_head, const void *v,
                    long long v_token, long long v_head, const float *z, long long z_token, const void *z_bias, float tau, float q_scale, int heads,
-                   int dk, int dv, const int32_t *seq_info, int num_seqs, float *state, long long slot_stride, int num_slots, float *out, int dtype,
-                   void *stream);
+                   int dk, int dv, const int32_t *seq_info, int num_seqs, int max_tokens_per_seq, float *state, long long slot_stride,
+                   int num_slots, float *out, void *workspace, size_t workspace_bytes, int dtype, void *stream);
 /* out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w * act(gate[t, h, :]) (gate rows g_token apart, NULL = no gate; act 0 = the gate
  * as it is, 1 = silu); o fp32 [tokens, heads, dv], out `dtype` [tokens, heads * dv]. */
 int tlb_head_norm_gate(const float *o, const void *w, float eps, const void *gate, long long g_token, int act, void *out, int tokens, int heads,

@@ -233,19 +233,47 @@ def test_decay_scan_against_the_recurrence_in_portions_batches_and_reused_slots(
     whole = blocks.decay_scan(q.to(dev), k.to(dev), v.to(dev), z.to(dev), zb.to(dev), tau=tau, q_scale=dk ** -0.5,
                               seq_info=torch.tensor([(0, 70, 0, 4), (70, 5, 0, 0), (75, 33, 0, 2)], dtype=torch.int32).to(dev), state=state)
     close(whole, want, tol)  # the slots' stale 9.0s were ignored at position 0
-    # the first two sequences again in portions, [40 | 2] then [3 | 30], in other slots and another order
+    # the first two sequences again in portions, [40 | 2] then [3 | 30], in other slots and another order.  A portion of up to 64
+    # tokens is one walk, bit for bit the same wherever it starts; the 70-token portion above ran as two segments cut at
+    # position 64, so its rows from there on differ from the walk by the rounding of one combination.
     first = blocks.decay_scan(torch.cat([q[0:40], q[70:72]]).to(dev), torch.cat([k[0:40], k[70:72]]).to(dev), torch.cat([v[0:40], v[70:72]]).to(dev),
                               torch.cat([z[0:40], z[70:72]]).to(dev), zb.to(dev), tau=tau, q_scale=dk ** -0.5,
-                              seq_info=torch.tensor([(0, 40, 0, 1), (40, 2, 0, 3)], dtype=torch.int32).to(dev), state=state)
+                              seq_info=torch.tensor([(0, 40, 0, 1), (40, 2, 0, 3)], dtype=torch.int32).to(dev), state=state, max_tokens=40)
     second = blocks.decay_scan(torch.cat([q[72:75], q[40:70]]).to(dev), torch.cat([k[72:75], k[40:70]]).to(dev), torch.cat([v[72:75], v[40:70]]).to(dev),
                                torch.cat([z[72:75], z[40:70]]).to(dev), zb.to(dev), tau=tau, q_scale=dk ** -0.5,
-                               seq_info=torch.tensor([(0, 3, 2, 3), (3, 30, 40, 1)], dtype=torch.int32).to(dev), state=state)
-    assert torch.equal(torch.cat([first[:40], second[3:]]), whole[:70]) and torch.equal(torch.cat([first[40:], second[:3]]), whole[70:75])
+                               seq_info=torch.tensor([(0, 3, 2, 3), (3, 30, 40, 1)], dtype=torch.int32).to(dev), state=state, max_tokens=30)
+    assert torch.equal(first[:40], whole[:40]) and torch.equal(second[3:27], whole[40:64])
+    close(second[27:], whole[64:70].double().cpu(), 2e-6)
+    assert torch.equal(torch.cat([first[40:], second[:3]]), whole[70:75])
     assert float(pool[:, :3].min()) == 9.0 and float(pool[:, -2:].min()) == 9.0  # the neighbours' columns are untouched
     # token by token from a slot that another sequence used
     rows = [blocks.decay_scan(q[t : t + 1].to(dev), k[t : t + 1].to(dev), v[t : t + 1].to(dev), z[t : t + 1].to(dev), zb.to(dev), tau=tau, q_scale=dk ** -0.5,
                               seq_info=torch.tensor([(0, 1, t - 75, 1)], dtype=torch.int32).to(dev), state=state) for t in range(75, 108)]
     assert torch.equal(torch.cat(rows), whole[75:])
+
+
+@pytest.mark.parametrize("start", [0, 1, 63, 64, 100])
+def test_long_portions_run_as_segments_cut_at_absolute_positions(dev, start):
+    """A 333-token portion that starts anywhere (after `start` tokens walked one by one): against the recurrence, and the
+    state it leaves against the walk's, through a batch whose other sequence is short."""
+    g = torch.Generator().manual_seed(start)
+    heads, dk, dv, tau, T = 2, 24, 40, 5.0, start + 333
+    q, k, v = (torch.randn(T + 3, heads, n, generator=g) for n in (dk, dk, dv))
+    z = 2 + torch.randn(T + 3, heads * dk, generator=g)
+    alpha = torch.sigmoid(z.double()).pow(1 / tau).view(T + 3, heads, dk)
+    want = O.decayed_linear_attention(q[:T].double() * dk ** -0.5, k[:T].double(), v[:T].double(), alpha[:T])
+    other = O.decayed_linear_attention(q[T:].double() * dk ** -0.5, k[T:].double(), v[T:].double(), alpha[T:])
+    state = torch.full((3, heads, dk, dv), 5.0, device=dev)
+    run = lambda lo, hi, rows, longest: blocks.decay_scan(q[lo:hi].to(dev), k[lo:hi].to(dev), v[lo:hi].to(dev), z[lo:hi].to(dev), None, tau=tau, q_scale=dk ** -0.5,
+                                                          seq_info=torch.tensor(rows, dtype=torch.int32).to(dev), state=state, max_tokens=longest)
+    head = [run(t, t + 1, [(0, 1, t, 2)], 1) for t in range(start)]
+    rest = run(start, T + 3, [(0, 333, start, 2), (333, 3, 0, 0)], 333)
+    close(torch.cat(head + [rest[:333]]), want, 2e-5)
+    close(rest[333:], other, 2e-5)
+    after = state[2].clone()
+    for t in range(T):  # the same sequence walked token by token in another slot
+        run(t, t + 1, [(0, 1, t, 1)], 1)
+    close(after, state[1].double().cpu(), 2e-5)
 
 
 def test_a_far_token_survives_in_the_state_only_as_much_as_the_decay_lets_it(dev):

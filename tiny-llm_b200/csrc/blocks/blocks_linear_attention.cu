@@ -3,12 +3,16 @@
 // Per sequence and head a matrix S [dk, dv] is carried from token to token:
 //     S <- diag(alpha_t) S + k_t v_t^T,      o_t = S^T (q_scale * q_t),
 //     alpha_t = sigmoid(z_t + bias)^(1 / tau) = exp(log_sigmoid(z_t + bias) / tau)        (per key channel)
-// The columns of S never mix, so a CTA owns 32 of them for one (sequence, head) and walks the sequence's new tokens in
-// order; 4 lanes share a column, each holding every 4th row of it in registers.  The tokens' q, k and decays are staged
-// 16 at a time in shared memory as fp32 (the decay is computed there, in fp32, from the fp32 logits).  A sequence that
-// starts at position 0 starts from zero, whatever its slot held; otherwise the slot is read, and in both cases written
-// back after the last token.  The order of every sum is fixed by the token and channel indices alone, so the result
-// does not depend on how the tokens were cut into steps or on the rest of the batch.
+// The columns of S never mix, so a CTA owns 32 of them for one (sequence, head) and walks tokens in order; 4 lanes share
+// a column, each holding every 4th row of it in registers.  The tokens' q, k and decays are staged 16 at a time in shared
+// memory as fp32 (the decay is computed there, in fp32, from the fp32 logits).  A sequence that starts at position 0
+// starts from zero, whatever its slot held; otherwise the slot is read, and in both cases written back after the last
+// token.  Single tokens and portions of up to 64 tokens are one walk.  A longer portion is cut into segments at the
+// multiples of 64 in ABSOLUTE positions, which run side by side: every segment's local end state from zero and the
+// product of its decays, then the start state of every segment by walking those in order (S' = decay * S + local), then
+// the outputs of every segment from its start state.  Every sum has an order fixed by token, channel and segment
+// indices alone; the cuts depend on positions only, so how a prompt was cut into steps changes the result by the
+// rounding of the combination at most.
 #include "blocks_common.cuh"
 
 namespace tlb {
@@ -16,31 +20,64 @@ namespace tlb {
 constexpr int kLaCols = 32;    // state columns per CTA
 constexpr int kLaLanes = 4;    // lanes per column
 constexpr int kLaTokens = 16;  // tokens staged at a time
+constexpr int kLaSegment = TLB_DECAY_SCAN_SEGMENT;  // positions per segment of a long portion
 
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
+// Segment c of a sequence's new tokens [p0, p0 + n): cut at the multiples of kLaSegment in ABSOLUTE positions, so that
+// where a prompt was cut into steps does not move the cuts.  Returns false when the sequence has no segment c.
+__device__ __forceinline__ bool la_segment(int p0, int n, int c, int &lo, int &hi, int &nseg) {
+    const int end = p0 + n, b0 = (p0 / kLaSegment + 1) * kLaSegment;
+    nseg = (n <= kLaSegment || end <= b0) ? 1 : 1 + (end - b0 + kLaSegment - 1) / kLaSegment;  // a short portion is never cut
+    if (c >= nseg) return false;
+    lo = c == 0 ? p0 : b0 + (c - 1) * kLaSegment;
+    hi = nseg == 1 ? end : min(end, c == 0 ? b0 : lo + kLaSegment);
+    return true;
+}
+
+// One kernel, three uses (pass):
+//   0  the whole portion of a sequence in one CTA per (head, column block): state from the slot (or zero at position 0),
+//      outputs, state back to the slot.  Single tokens and short portions.
+//   1  segment c alone from a ZERO state, no outputs: its local end state and the product of its decays go to the
+//      workspace (the last segment of a sequence is skipped: nobody needs its local state).
+//   3  segment c from the start state that decay_combine_kernel left in the workspace: outputs; the last segment writes
+//      the slot.
 template <typename T, int KR /* rows per lane: dk <= 4 * KR */>
 __global__ void __launch_bounds__(kLaCols * kLaLanes)
 decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, const T *__restrict__ k, long long k_token, long long k_head,
                   const T *__restrict__ v, long long v_token, long long v_head, const float *__restrict__ z, long long z_token,
                   const T *__restrict__ z_bias, float inv_tau, float q_scale, int heads, int dk, int dv, const int32_t *__restrict__ seq_info,
-                  float *__restrict__ state, long long slot_stride, int num_slots, float *__restrict__ out) {
+                  float *__restrict__ state, long long slot_stride, int num_slots, float *__restrict__ out, int pass, int max_segments,
+                  float *__restrict__ seg_state, float *__restrict__ seg_decay) {
     __shared__ float sq[kLaTokens * 4 * KR], sk[kLaTokens * 4 * KR], sa[kLaTokens * 4 * KR];
     __shared__ float sv[kLaTokens * kLaCols];
-    const int s = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * kLaCols;
-    const int first = seq_info[s * 4 + 0], count = seq_info[s * 4 + 1], start = seq_info[s * 4 + 2], slot = seq_info[s * 4 + 3];
-    const int c = threadIdx.x / kLaLanes, r = threadIdx.x % kLaLanes;
-    const int col = col0 + c;
+    __shared__ float sprod[4 * KR];
+    const int colblocks = (dv + kLaCols - 1) / kLaCols;
+    const int s = blockIdx.x, head = blockIdx.y / colblocks, col0 = (blockIdx.y % colblocks) * kLaCols, c = blockIdx.z;
+    const int seq_first = seq_info[s * 4 + 0], seq_count = seq_info[s * 4 + 1], start = seq_info[s * 4 + 2], slot = seq_info[s * 4 + 3];
+    int lo = start, hi = start + seq_count, nseg = 1;
+    if (pass != 0 && !la_segment(start, seq_count, c, lo, hi, nseg)) return;
+    if (pass == 1 && c == nseg - 1) return;
+    const int first = seq_first + (lo - start), count = hi - lo;
+    const int cidx = threadIdx.x / kLaLanes, r = threadIdx.x % kLaLanes;
+    const int col = col0 + cidx;
     const bool col_ok = col < dv;
     const bool slot_ok = slot >= 0 && slot < num_slots;
     float *mine = state + (size_t)(slot_ok ? slot : 0) * slot_stride + (size_t)head * dk * dv;
+    float *seg = seg_state ? seg_state + (((size_t)s * max_segments + c) * heads + head) * dk * dv : nullptr;
+    const bool from_slot = pass == 0 || (pass == 3 && c == 0);   // else: zero (pass 1) or the combined start state (pass 3)
+    const bool to_slot = pass == 0 || (pass == 3 && c == nseg - 1);
 
     float S[KR];
 #pragma unroll
     for (int i = 0; i < KR; ++i) {
         int row = r + kLaLanes * i;
-        S[i] = (start > 0 && slot_ok && col_ok && row < dk) ? mine[(size_t)row * dv + col] : 0.f;
+        bool ok = col_ok && row < dk;
+        if (from_slot) S[i] = (lo > 0 && slot_ok && ok) ? mine[(size_t)row * dv + col] : 0.f;
+        else S[i] = (pass == 3 && ok) ? seg[(size_t)row * dv + col] : 0.f;
     }
+    if (pass == 1)
+        for (int d = threadIdx.x; d < dk; d += blockDim.x) sprod[d] = 1.f;
     for (int t0 = 0; t0 < count; t0 += kLaTokens) {
         const int n = min(kLaTokens, count - t0);
         __syncthreads();
@@ -57,29 +94,74 @@ decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
             sv[e] = col0 + d < dv ? to_f(v[(size_t)(first + t0 + j) * v_token + (size_t)head * v_head + col0 + d]) : 0.f;
         }
         __syncthreads();
+        if (pass == 1) {  // the segment's decay product per key channel, in token order
+            for (int d = threadIdx.x; d < dk; d += blockDim.x) {
+                float p = sprod[d];
+                for (int j = 0; j < n; ++j) p *= sa[j * 4 * KR + d];
+                sprod[d] = p;
+            }
+        }
         for (int j = 0; j < n; ++j) {
-            const float vj = sv[j * kLaCols + c];
+            const float vj = sv[j * kLaCols + cidx];
             const float *qa = sq + j * 4 * KR, *ka = sk + j * 4 * KR, *aa = sa + j * 4 * KR;
-            float o = 0.f;
+            float o0 = 0.f, o1 = 0.f;
 #pragma unroll
-            for (int i = 0; i < KR; ++i) {
+            for (int i = 0; i < KR; i += 2) {
                 int row = r + kLaLanes * i;
                 if (row < dk) {
                     S[i] = fmaf(aa[row], S[i], ka[row] * vj);
-                    o = fmaf(qa[row], S[i], o);
+                    o0 = fmaf(qa[row], S[i], o0);
+                }
+                if (row + kLaLanes < dk) {
+                    S[i + 1] = fmaf(aa[row + kLaLanes], S[i + 1], ka[row + kLaLanes] * vj);
+                    o1 = fmaf(qa[row + kLaLanes], S[i + 1], o1);
                 }
             }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            if (r == 0 && col_ok) out[((size_t)(first + t0 + j) * heads + head) * dv + col] = o;
+            if (pass != 1) {
+                float o = o0 + o1;
+                o += __shfl_xor_sync(0xffffffffu, o, 1);
+                o += __shfl_xor_sync(0xffffffffu, o, 2);
+                if (r == 0 && col_ok) out[((size_t)(first + t0 + j) * heads + head) * dv + col] = o;
+            }
         }
     }
-    if (slot_ok && col_ok) {
+    float *dst = to_slot ? (slot_ok ? mine : nullptr) : (pass == 1 ? seg : nullptr);
+    if (dst != nullptr && col_ok) {
 #pragma unroll
         for (int i = 0; i < KR; ++i) {
             int row = r + kLaLanes * i;
-            if (row < dk) mine[(size_t)row * dv + col] = S[i];
+            if (row < dk) dst[(size_t)row * dv + col] = S[i];
         }
+    }
+    if (pass == 1 && col0 == 0) {
+        __syncthreads();
+        float *pd = seg_decay + (((size_t)s * max_segments + c) * heads + head) * dk;
+        for (int d = threadIdx.x; d < dk; d += blockDim.x) pd[d] = sprod[d];
+    }
+}
+
+// Between the two passes: walk a sequence's segments in order, S_start[c + 1] = decay[c] * S_start[c] + local[c], and leave
+// every segment's START state where its local end state was.  One thread per state element, (sequence, head) per blockIdx.
+__global__ void __launch_bounds__(256)
+decay_combine_kernel(const int32_t *__restrict__ seq_info, const float *__restrict__ state, long long slot_stride, int num_slots, int heads, int dk,
+                     int dv, int max_segments, float *__restrict__ seg_state, const float *__restrict__ seg_decay) {
+    const int s = blockIdx.x, head = blockIdx.y;
+    const int count = seq_info[s * 4 + 1], start = seq_info[s * 4 + 2], slot = seq_info[s * 4 + 3];
+    int lo, hi, nseg;
+    la_segment(start, count, 0, lo, hi, nseg);
+    if (nseg <= 1) return;
+    const bool slot_ok = slot >= 0 && slot < num_slots;
+    const float *mine = state + (size_t)(slot_ok ? slot : 0) * slot_stride + (size_t)head * dk * dv;
+    for (int e = blockIdx.z * blockDim.x + threadIdx.x; e < dk * dv; e += gridDim.z * blockDim.x) {
+        const int row = e / dv;
+        float S = (start > 0 && slot_ok) ? mine[e] : 0.f;
+        for (int c = 0; c + 1 < nseg; ++c) {
+            float *cell = seg_state + (((size_t)s * max_segments + c) * heads + head) * dk * dv + e;
+            float local = *cell;
+            *cell = S;
+            S = fmaf(seg_decay[(((size_t)s * max_segments + c) * heads + head) * dk + row], S, local);
+        }
+        seg_state[(((size_t)s * max_segments + (nseg - 1)) * heads + head) * dk * dv + e] = S;
     }
 }
 
@@ -114,24 +196,53 @@ using namespace tlb;
 
 extern "C" {
 
+size_t tlb_decay_scan_workspace(int num_seqs, int max_tokens_per_seq, int heads, int dk, int dv) {
+    if (max_tokens_per_seq <= kLaSegment) return 0;
+    size_t segs = (size_t)num_seqs * (2 + (max_tokens_per_seq - 1) / kLaSegment);
+    return segs * heads * ((size_t)dk * dv + dk) * sizeof(float);
+}
+
 int tlb_decay_scan(const void *q, long long q_token, long long q_head, const void *k, long long k_token, long long k_head, const void *v,
                    long long v_token, long long v_head, const float *z, long long z_token, const void *z_bias, float tau, float q_scale, int heads,
-                   int dk, int dv, const int32_t *seq_info, int num_seqs, float *state, long long slot_stride, int num_slots, float *out, int dtype,
-                   void *stream) {
+                   int dk, int dv, const int32_t *seq_info, int num_seqs, int max_tokens_per_seq, float *state, long long slot_stride, int num_slots,
+                   float *out, void *workspace, size_t workspace_bytes, int dtype, void *stream) {
     if (num_seqs <= 0) return TL_OK;
-    if (!q || !k || !v || !z || !seq_info || !state || !out || heads <= 0 || dk <= 0 || dv <= 0 || !(tau > 0.f) || num_slots <= 0)
+    if (!q || !k || !v || !z || !seq_info || !state || !out || heads <= 0 || dk <= 0 || dv <= 0 || !(tau > 0.f) || num_slots <= 0 ||
+        max_tokens_per_seq <= 0)
         return tl::fail(TL_EINVAL, "decay_scan: bad argument");
     if (dk > 128) return tl::fail(TL_EINVAL, "decay_scan: key size %d > 128", dk);
-    dim3 grid(num_seqs, heads, ceil_div(dv, kLaCols));
+    // portions longer than a segment are cut at absolute multiples of the segment length and run in three passes
+    const bool segmented = max_tokens_per_seq > kLaSegment;
+    const int max_segments = segmented ? 2 + (max_tokens_per_seq - 1) / kLaSegment : 1;
+    float *seg_state = nullptr, *seg_decay = nullptr;
+    if (segmented) {
+        if (!workspace || workspace_bytes < tlb_decay_scan_workspace(num_seqs, max_tokens_per_seq, heads, dk, dv))
+            return tl::fail(TL_EWORKSPACE, "decay_scan: workspace missing or too small");
+        seg_state = (float *)workspace;
+        seg_decay = seg_state + (size_t)num_seqs * max_segments * heads * dk * dv;
+    }
+    const int colblocks = ceil_div(dv, kLaCols);
     cudaStream_t st = as_stream(stream);
     int kr = ceil_div(dk, kLaLanes);
-#define TLB_DS(KRV)                                                                                                                               \
-    decay_scan_kernel<T, KRV><<<grid, kLaCols * kLaLanes, 0, st>>>((const T *)q, q_token, q_head, (const T *)k, k_token, k_head, (const T *)v, v_token, \
-                                                                  v_head, z, z_token, (const T *)z_bias, 1.0f / tau, q_scale, heads, dk, dv, seq_info, \
-                                                                  state, slot_stride, num_slots, out)
-    TLB_DISPATCH(dtype, "decay_scan", if (kr <= 8) TLB_DS(8); else if (kr <= 16) TLB_DS(16); else TLB_DS(32));
+#define TLB_DS_K(KRV, PASS, GZ)                                                                                                                    \
+    decay_scan_kernel<T, KRV><<<dim3(num_seqs, heads * colblocks, GZ), kLaCols * kLaLanes, 0, st>>>(                                                \
+        (const T *)q, q_token, q_head, (const T *)k, k_token, k_head, (const T *)v, v_token, v_head, z, z_token, (const T *)z_bias, 1.0f / tau, q_scale, \
+        heads, dk, dv, seq_info, state, slot_stride, num_slots, out, PASS, max_segments, seg_state, seg_decay)
+#define TLB_DS(PASS, GZ) TLB_DISPATCH(dtype, "decay_scan", if (kr <= 8) TLB_DS_K(8, PASS, GZ); else if (kr <= 16) TLB_DS_K(16, PASS, GZ); else TLB_DS_K(32, PASS, GZ))
+    if (!segmented) {
+        TLB_DS(0, 1);
+        TL_LAUNCH_CHECK("decay_scan");
+        return TL_OK;
+    }
+    TLB_DS(1, max_segments);
+    TL_LAUNCH_CHECK("decay_scan (local states)");
+    decay_combine_kernel<<<dim3(num_seqs, heads, ceil_div(dk * dv, 256 * 4)), 256, 0, st>>>(seq_info, state, slot_stride, num_slots, heads, dk, dv,
+                                                                                           max_segments, seg_state, seg_decay);
+    TL_LAUNCH_CHECK("decay_scan (combine)");
+    TLB_DS(3, max_segments);
+    TL_LAUNCH_CHECK("decay_scan (outputs)");
 #undef TLB_DS
-    TL_LAUNCH_CHECK("decay_scan");
+#undef TLB_DS_K
     return TL_OK;
 }
 

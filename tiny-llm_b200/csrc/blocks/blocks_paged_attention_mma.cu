@@ -3,7 +3,8 @@
 //
 // A CTA takes 32 query rows = a run of consecutive tokens of one sequence x the query heads of ONE key/value head (up to
 // 32 of them) and streams every 32-key tile of that head through shared memory once for all of them: keys into one
-// buffer, values into another (cp.async, 16 bytes a piece).  Per key tile, with 8 warps:
+// buffer, values into another (cp.async, 16 bytes a piece), each twice, so that the next tile loads while this one is
+// computed.  Per key tile, with 8 warps:
 //   1. scores:  the 32 x 32 block S = Q K^T is 2 x 4 blocks of 16 x 8, one per warp (two accumulator sets alternate over
 //               the reduction so that consecutive MMAs do not wait on each other);
 //   2. softmax: each warp owns 4 rows, 8 lanes per row, 4 keys per lane: scale, soft cap, mask, running maximum / sum
@@ -60,9 +61,9 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
                            bf16 *__restrict__ out, long long o_token, long long o_head, int k_stride, int v_stride /* shared-memory row strides */) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16 *sq = reinterpret_cast<bf16 *>(smem_raw);              // [32][k_stride]
-    bf16 *sk = sq + kGRows * k_stride;                          // [32][k_stride]
-    bf16 *sv = sk + kGKeys * k_stride;                          // [32][v_stride]
-    bf16 *sp = sv + kGKeys * v_stride;                          // [32][kGSP]
+    bf16 *sk0 = sq + kGRows * k_stride;                         // [2][32][k_stride]
+    bf16 *sv0 = sk0 + 2 * kGKeys * k_stride;                    // [2][32][v_stride]
+    bf16 *sp = sv0 + 2 * kGKeys * v_stride;                     // [32][kGSP]
     float *ss = reinterpret_cast<float *>(sp + kGRows * kGSP);  // [32][kGSS]
     float *s_alpha = ss + kGRows * kGSS;                        // [32]
     float *s_l = s_alpha + kGRows;                              // [32]
@@ -78,7 +79,7 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
     const int k_pieces = dk / 8, v_pieces = dv / 8;  // 16-byte pieces of a key / value row
 
     // zero everything once: padding columns of Q, K and V must read as zero in every product
-    for (int i = threadIdx.x; i < ((kGRows + kGKeys) * k_stride + kGKeys * v_stride) / 8; i += blockDim.x)
+    for (int i = threadIdx.x; i < ((kGRows + 2 * kGKeys) * k_stride + 2 * kGKeys * v_stride) / 8; i += blockDim.x)
         reinterpret_cast<uint4 *>(sq)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
     for (int r = warp; r < kGRows; r += kGWarps) {  // row = token-in-tile * hp + head-in-group
@@ -97,22 +98,21 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
     const int n_tiles = (hi - lo) / kGKeys + 1;
     const size_t k_off = (size_t)g * dk, v_off = (size_t)kv_heads * dk + (size_t)g * dv;
 
-    auto stage = [&](int tile) {
+    auto stage = [&](int tile, int buf) {
+        bf16 *sk = sk0 + buf * kGKeys * k_stride, *sv = sv0 + buf * kGKeys * v_stride;
         int k0 = lo + tile * kGKeys;
         int page = table[k0 / page_size];
         bool ok = page >= 0 && page < num_pages;
         int valid = ok ? min(kGKeys, hi - k0 + 1) : 0;
         const bf16 *src = slab + ((size_t)(ok ? page : 0) * page_size + (k0 % page_size)) * row_width;
-        for (int j = warp; j < kGKeys; j += kGWarps) {  // a warp copies whole rows
-            bf16 *dkp = sk + j * k_stride, *dvp = sv + j * v_stride;
-            const bf16 *gk = src + (size_t)j * row_width + k_off, *gv = src + (size_t)j * row_width + v_off;
-            if (j < valid) {
-                for (int piece = lane; piece < k_pieces; piece += 32) g_cp16(dkp + piece * 8, gk + piece * 8);
-                for (int piece = lane; piece < v_pieces; piece += 32) g_cp16(dvp + piece * 8, gv + piece * 8);
-            } else {
-                for (int piece = lane; piece < k_pieces; piece += 32) *reinterpret_cast<uint4 *>(dkp + piece * 8) = make_uint4(0, 0, 0, 0);
-                for (int piece = lane; piece < v_pieces; piece += 32) *reinterpret_cast<uint4 *>(dvp + piece * 8) = make_uint4(0, 0, 0, 0);
-            }
+        const int per_row = k_pieces + v_pieces;
+        for (int idx = threadIdx.x; idx < kGKeys * per_row; idx += blockDim.x) {  // one 16-byte piece of a key or value row each
+            int j = idx / per_row, piece = idx - j * per_row;
+            bool is_v = piece >= k_pieces;
+            int col = (is_v ? piece - k_pieces : piece) * 8;
+            bf16 *dst = is_v ? sv + j * v_stride + col : sk + j * k_stride + col;
+            if (j < valid) g_cp16(dst, src + (size_t)j * row_width + (is_v ? v_off : k_off) + col);
+            else *reinterpret_cast<uint4 *>(dst) = make_uint4(0, 0, 0, 0);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -132,11 +132,14 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
     for (int i = 0; i < 2 * PAIRS; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
     const int ksteps = (dk + 15) / 16;
+    __syncthreads();  // the zero fill is done before the first copies land
+    stage(0, 0);
     for (int tile = 0; tile < n_tiles; ++tile) {
-        __syncthreads();  // every warp is done with the previous tile (and, first time, the zero fill and the queries are in place)
-        stage(tile);
+        const int buf = tile & 1;
+        const bf16 *sk = sk0 + buf * kGKeys * k_stride, *sv = sv0 + buf * kGKeys * v_stride;
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();
+        __syncthreads();  // this tile has landed, and every warp is done with the previous one: its buffer may be refilled
+        if (tile + 1 < n_tiles) stage(tile + 1, buf ^ 1);
 
         // 1. scores: this warp's 16 rows x 8 keys
         {
@@ -282,7 +285,7 @@ int tlb_paged_attention_mma(const void *q, long long q_token, long long q_head, 
     int pairs = g_pairs(dv);
     int k_stride = ceil_div(dk, 16) * 16 + 8;  // (stride / 8) odd: conflict-free ldmatrix rows
     int v_stride = 64 * pairs + 8;
-    size_t smem = (size_t)((kGRows + kGKeys) * k_stride + kGKeys * v_stride) * 2 + kGRows * kGSP * 2 + (size_t)kGRows * kGSS * 4 + 2 * kGRows * 4;
+    size_t smem = (size_t)((kGRows + 2 * kGKeys) * k_stride + 2 * kGKeys * v_stride) * 2 + kGRows * kGSP * 2 + (size_t)kGRows * kGSS * 4 + 2 * kGRows * 4;
     dim3 grid(num_tiles, kv_heads * ceil_div(group, hp));
     cudaStream_t st = as_stream(stream);
 #define TLB_PAM(P)                                                                                                                               \

@@ -47,7 +47,9 @@ _SIGNATURES = {
     "tlb_paged_attention_mma_supported": (_I, [_I, _I, _I, _I]),
     "tlb_paged_attention_mma": (_I, [_VP, _LL, _LL, _VP, _I, _I, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _F, _I, _VP, _LL, _VP, _LL, _LL, _VP]),
     "tlb_kv_prepare": (_I, [_VP, _LL, _LL, _I, _VP, _VP, _LL, _LL, _VP, _LL, _LL, _I, _I, _I, _VP, _F, _VP, _VP, _VP, _I, _I, _I, _VP, _I, _I, _VP]),
-    "tlb_decay_scan": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _VP, _F, _F, _I, _I, _I, _VP, _I, _VP, _LL, _I, _VP, _I, _VP]),
+    "tlb_decay_scan_workspace": (ctypes.c_size_t, [_I, _I, _I, _I, _I]),
+    "tlb_decay_scan": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _VP, _F, _F, _I, _I, _I, _VP, _I, _I, _VP, _LL, _I, _VP, _VP, ctypes.c_size_t,
+                            _I, _VP]),
     "tlb_head_norm_gate": (_I, [_VP, _VP, _F, _VP, _LL, _I, _VP, _I, _I, _I, _I, _VP]),
     "tlb_moe_max_rows": (_LL, [_I, _I, _I, _I]),
     "tlb_moe_sort": (_I, [_VP, _I, _I, _I, _I, _VP, _VP, _VP, _VP]),
@@ -451,10 +453,11 @@ def paged_attention(q, slab, block_table, tiles, tok_pos, *, kv_heads: int, dv: 
     return out
 
 
-def decay_scan(q, k, v, z, z_bias, *, tau: float, q_scale: float, seq_info, state, out=None):
+def decay_scan(q, k, v, z, z_bias, *, tau: float, q_scale: float, seq_info, state, out=None, max_tokens: int | None = None):
     """Linear attention with per-channel decay ``sigmoid(z + z_bias)^(1/tau)``: ``q, k [T, H, dk]``, ``v [T, H, dv]`` views,
     ``z [T, H * dk]`` fp32, ``seq_info [S, 4]`` int32 (first token, count, start position, slot), ``state [slots, H, dk, dv]``
-    fp32 (a view whose slots may be further apart) -> fp32 ``[T, H, dv]``."""
+    fp32 (a view whose slots may be further apart) -> fp32 ``[T, H, dv]``.  ``max_tokens``: the largest count in
+    ``seq_info`` (default: all tokens); portions longer than a segment run as parallel segments over a workspace."""
     _gpu("decay_scan", q, k, v, z, z_bias, seq_info, state, out)
     T, H, dk = q.shape
     dv = v.shape[2]
@@ -468,9 +471,13 @@ def decay_scan(q, k, v, z, z_bias, *, tau: float, q_scale: float, seq_info, stat
         raise RuntimeError("decay_scan: seq_info must be int32 [S, 4]")
     if out is None:
         out = torch.empty((T, H, dv), dtype=torch.float32, device=q.device)
-    _check(library().tlb_decay_scan(_ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1), _ptr(v), v.stride(0), v.stride(1), _ptr(z),
-                                    z.stride(0), _ptr(z_bias), float(tau), float(q_scale), H, dk, dv, _ptr(seq_info), seq_info.shape[0], _ptr(state),
-                                    state.stride(0), state.shape[0], _ptr(out), _code(q.dtype), _stream(q)))
+    longest = T if max_tokens is None else max(1, min(int(max_tokens), T))
+    lib = library()
+    nbytes = int(lib.tlb_decay_scan_workspace(seq_info.shape[0], longest, H, dk, dv))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
+    _check(lib.tlb_decay_scan(_ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1), _ptr(v), v.stride(0), v.stride(1), _ptr(z),
+                              z.stride(0), _ptr(z_bias), float(tau), float(q_scale), H, dk, dv, _ptr(seq_info), seq_info.shape[0], longest, _ptr(state),
+                              state.stride(0), state.shape[0], _ptr(out), _ptr(ws), nbytes, _code(q.dtype), _stream(q)))
     return out
 
 

@@ -39,5 +39,5 @@ class DecayedLinearAttention:
         H = self.heads
         z = linear_wide(a1.contiguous(), self.w_a2)  # fp32 decay logits
         o = blocks.decay_scan(q.unflatten(1, (H, self.dim)), k.unflatten(1, (H, self.dim)), v.unflatten(1, (H, self.vdim)), z, self.a2_bias,
-                              tau=self.tau, q_scale=self.dim ** -0.5, seq_info=plan.seq_info, state=state)
+                              tau=self.tau, q_scale=self.dim ** -0.5, seq_info=plan.seq_info, state=state, max_tokens=plan.max_tokens)
         return linear_wide(blocks.head_norm_gate(o, self.norm_weight, self.eps, gate, act=1), self.w_o)

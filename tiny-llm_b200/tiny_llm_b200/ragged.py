@@ -122,6 +122,7 @@ class RaggedPlan:
         self.max_context = max(o.offset for o in owners)  # the longest sequence after this step's append
         self.want_counts = [len(x) for x in wants]
         self.starts = starts
+        self.max_tokens = max(len(e.tokens) for e in entries)  # the longest entry of the step
         self.owners = owners
         for o in owners:  # from here on the step runs: what it consumes cannot be taken back from a recurrent state
             if hasattr(o, "ran_offset"):
