@@ -127,7 +127,7 @@ int tlb_kv_prepare(void *q, long long q_token, long long q_head, int heads, cons
  * seq_info [num_seqs, 4] int32: first flat token, token count, position of the first token, state slot.  A sequence at
  * position 0 starts from zero; the slot (state + slot * slot_stride floats, [heads, dk, dv]) is written after the last
  * token.  q, k [T, heads, dk], v [T, heads, dv] views (strides in elements), z [T, heads * dk] fp32 rows z_token apart,
- * z_bias `dtype` or NULL, out [T, heads, dv] fp32 contiguous.  dk <= 128.
+ * z_bias `dtype` or NULL, out [T, heads, dv] fp32 contiguous.  dk <= 256.
  * max_tokens_per_seq = the largest token count in seq_info (known to the host).  Up to TLB_DECAY_SCAN_SEGMENT tokens a
  * sequence is walked in one go.  Longer portions are cut at the multiples of the segment length in absolute positions and
  * run in three launches (every segment's local end state and decay product from a zero state; the segments' start

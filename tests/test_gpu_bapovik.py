@@ -213,7 +213,7 @@ def test_keys_and_values_land_on_their_slots_with_per_head_norms(dev, dtype, nor
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,dk,dv", [(2, 16, 32), (3, 12, 40), (1, 128, 64), (2, 33, 7)])
+@pytest.mark.parametrize("heads,dk,dv", [(2, 16, 32), (3, 12, 40), (1, 128, 64), (2, 33, 7), (1, 200, 36)])
 def test_decay_scan_against_the_recurrence_in_portions_batches_and_reused_slots(dev, dtype, heads, dk, dv):
     g = torch.Generator().manual_seed(dk)
     lens = [70, 5, 33]

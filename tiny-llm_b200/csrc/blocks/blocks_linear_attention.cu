@@ -4,7 +4,7 @@
 //     S <- diag(alpha_t) S + k_t v_t^T,      o_t = S^T (q_scale * q_t),
 //     alpha_t = sigmoid(z_t + bias)^(1 / tau) = exp(log_sigmoid(z_t + bias) / tau)        (per key channel)
 // The columns of S never mix, so a CTA owns 32 of them for one (sequence, head) and walks tokens in order; 4 lanes share
-// a column, each holding every 4th row of it in registers.  The tokens' q, k and decays are staged 16 at a time in shared
+// a column, each holding every 4th row of it in registers.  The tokens' q, k and decays are staged 16 (8 for dk > 128) at a time in shared
 // memory as fp32 (the decay is computed there, in fp32, from the fp32 logits).  A sequence that starts at position 0
 // starts from zero, whatever its slot held; otherwise the slot is read, and in both cases written back after the last
 // token.  Single tokens and portions of up to 64 tokens are one walk.  A longer portion is cut into segments at the
@@ -19,7 +19,6 @@ namespace tlb {
 
 constexpr int kLaCols = 32;    // state columns per CTA
 constexpr int kLaLanes = 4;    // lanes per column
-constexpr int kLaTokens = 16;  // tokens staged at a time
 constexpr int kLaSegment = TLB_DECAY_SCAN_SEGMENT;  // positions per segment of a long portion
 
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
@@ -42,14 +41,14 @@ __device__ __forceinline__ bool la_segment(int p0, int n, int c, int &lo, int &h
 //      workspace (the last segment of a sequence is skipped: nobody needs its local state).
 //   3  segment c from the start state that decay_combine_kernel left in the workspace: outputs; the last segment writes
 //      the slot.
-template <typename T, int KR /* rows per lane: dk <= 4 * KR */>
+template <typename T, int KR /* rows per lane: dk <= 4 * KR */, int kLaTokens /* tokens staged at a time */>
 __global__ void __launch_bounds__(kLaCols * kLaLanes)
 decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, const T *__restrict__ k, long long k_token, long long k_head,
                   const T *__restrict__ v, long long v_token, long long v_head, const float *__restrict__ z, long long z_token,
                   const T *__restrict__ z_bias, float inv_tau, float q_scale, int heads, int dk, int dv, const int32_t *__restrict__ seq_info,
                   float *__restrict__ state, long long slot_stride, int num_slots, float *__restrict__ out, int pass, int max_segments,
                   float *__restrict__ seg_state, float *__restrict__ seg_decay) {
-    __shared__ float sq[kLaTokens * 4 * KR], sk[kLaTokens * 4 * KR], sa[kLaTokens * 4 * KR];
+    __shared__ float4 sx[kLaTokens * 4 * KR];  // per token and key channel: (decay, k, scaled q, -), one 16-byte read per row
     __shared__ float sv[kLaTokens * kLaCols];
     __shared__ float sprod[4 * KR];
     const int colblocks = (dv + kLaCols - 1) / kLaCols;
@@ -84,10 +83,9 @@ decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
         for (int e = threadIdx.x; e < n * dk; e += blockDim.x) {
             int j = e / dk, d = e - j * dk;
             size_t tok = (size_t)(first + t0 + j);
-            sq[j * 4 * KR + d] = to_f(q[tok * q_token + (size_t)head * q_head + d]) * q_scale;
-            sk[j * 4 * KR + d] = to_f(k[tok * k_token + (size_t)head * k_head + d]);
             float logit = z[tok * z_token + (size_t)head * dk + d] + (z_bias ? to_f(z_bias[(size_t)head * dk + d]) : 0.f);
-            sa[j * 4 * KR + d] = expf(log_sigmoid(logit) * inv_tau);
+            sx[j * 4 * KR + d] = make_float4(expf(log_sigmoid(logit) * inv_tau), to_f(k[tok * k_token + (size_t)head * k_head + d]),
+                                             to_f(q[tok * q_token + (size_t)head * q_head + d]) * q_scale, 0.f);
         }
         for (int e = threadIdx.x; e < n * kLaCols; e += blockDim.x) {
             int j = e / kLaCols, d = e - j * kLaCols;
@@ -97,24 +95,26 @@ decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
         if (pass == 1) {  // the segment's decay product per key channel, in token order
             for (int d = threadIdx.x; d < dk; d += blockDim.x) {
                 float p = sprod[d];
-                for (int j = 0; j < n; ++j) p *= sa[j * 4 * KR + d];
+                for (int j = 0; j < n; ++j) p *= sx[j * 4 * KR + d].x;
                 sprod[d] = p;
             }
         }
         for (int j = 0; j < n; ++j) {
             const float vj = sv[j * kLaCols + cidx];
-            const float *qa = sq + j * 4 * KR, *ka = sk + j * 4 * KR, *aa = sa + j * 4 * KR;
+            const float4 *xa = sx + j * 4 * KR;
             float o0 = 0.f, o1 = 0.f;
 #pragma unroll
             for (int i = 0; i < KR; i += 2) {
                 int row = r + kLaLanes * i;
                 if (row < dk) {
-                    S[i] = fmaf(aa[row], S[i], ka[row] * vj);
-                    o0 = fmaf(qa[row], S[i], o0);
+                    float4 x = xa[row];
+                    S[i] = fmaf(x.x, S[i], x.y * vj);
+                    o0 = fmaf(x.z, S[i], o0);
                 }
                 if (row + kLaLanes < dk) {
-                    S[i + 1] = fmaf(aa[row + kLaLanes], S[i + 1], ka[row + kLaLanes] * vj);
-                    o1 = fmaf(qa[row + kLaLanes], S[i + 1], o1);
+                    float4 x = xa[row + kLaLanes];
+                    S[i + 1] = fmaf(x.x, S[i + 1], x.y * vj);
+                    o1 = fmaf(x.z, S[i + 1], o1);
                 }
             }
             if (pass != 1) {
@@ -210,7 +210,7 @@ int tlb_decay_scan(const void *q, long long q_token, long long q_head, const voi
     if (!q || !k || !v || !z || !seq_info || !state || !out || heads <= 0 || dk <= 0 || dv <= 0 || !(tau > 0.f) || num_slots <= 0 ||
         max_tokens_per_seq <= 0)
         return tl::fail(TL_EINVAL, "decay_scan: bad argument");
-    if (dk > 128) return tl::fail(TL_EINVAL, "decay_scan: key size %d > 128", dk);
+    if (dk > 256) return tl::fail(TL_EINVAL, "decay_scan: key size %d > 256", dk);
     // portions longer than a segment are cut at absolute multiples of the segment length and run in three passes
     const bool segmented = max_tokens_per_seq > kLaSegment;
     const int max_segments = segmented ? 2 + (max_tokens_per_seq - 1) / kLaSegment : 1;
@@ -225,10 +225,10 @@ int tlb_decay_scan(const void *q, long long q_token, long long q_head, const voi
     cudaStream_t st = as_stream(stream);
     int kr = ceil_div(dk, kLaLanes);
 #define TLB_DS_K(KRV, PASS, GZ)                                                                                                                    \
-    decay_scan_kernel<T, KRV><<<dim3(num_seqs, heads * colblocks, GZ), kLaCols * kLaLanes, 0, st>>>(                                                \
+    decay_scan_kernel<T, KRV, (KRV > 32 ? 8 : 16)><<<dim3(num_seqs, heads * colblocks, GZ), kLaCols * kLaLanes, 0, st>>>(                                                \
         (const T *)q, q_token, q_head, (const T *)k, k_token, k_head, (const T *)v, v_token, v_head, z, z_token, (const T *)z_bias, 1.0f / tau, q_scale, \
         heads, dk, dv, seq_info, state, slot_stride, num_slots, out, PASS, max_segments, seg_state, seg_decay)
-#define TLB_DS(PASS, GZ) TLB_DISPATCH(dtype, "decay_scan", if (kr <= 8) TLB_DS_K(8, PASS, GZ); else if (kr <= 16) TLB_DS_K(16, PASS, GZ); else TLB_DS_K(32, PASS, GZ))
+#define TLB_DS(PASS, GZ) TLB_DISPATCH(dtype, "decay_scan", if (kr <= 8) TLB_DS_K(8, PASS, GZ); else if (kr <= 16) TLB_DS_K(16, PASS, GZ); else if (kr <= 32) TLB_DS_K(32, PASS, GZ); else TLB_DS_K(64, PASS, GZ))
     if (!segmented) {
         TLB_DS(0, 1);
         TL_LAUNCH_CHECK("decay_scan");

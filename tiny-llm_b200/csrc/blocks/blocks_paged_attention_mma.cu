@@ -9,6 +9,7 @@
 //               the reduction so that consecutive MMAs do not wait on each other);
 //   2. softmax: each warp owns 4 rows, 8 lanes per row, 4 keys per lane: scale, soft cap, mask, running maximum / sum
 //               (a sink starts them at 0 / 1), P = exp(S - m) as bf16, rescale factor;
+//               what a row sees is a key range worked out once per row, the cap's tanh is the hardware approximation;
 //   3. values:  O[32 x dv] += P V, warp = (16-row half, quarter of the value columns).
 // A row's arithmetic depends only on its own position (32-aligned key tiles in ascending order): what else is in the
 // CTA, the launch or the batch does not change its result, nor does where a prompt was cut.
@@ -44,11 +45,11 @@ __device__ __forceinline__ void g_cp16(void *dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
 }
 
-__device__ __forceinline__ bool g_visible(int p, int key, int mask, int size) {
-    if (key > p) return false;
-    if (mask == 1) return p - key < size;
-    if (mask == 2) return p / size == key / size;
-    return true;
+// tanh by the hardware approximation (relative error about 2^-11): the probabilities it feeds are rounded to bf16 anyway
+__device__ __forceinline__ float g_tanh(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 // PAIRS = pairs of 8-column value tiles per warp (the warp's quarter of the value columns = 16 * PAIRS columns).
@@ -61,9 +62,9 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
                            bf16 *__restrict__ out, long long o_token, long long o_head, int k_stride, int v_stride /* shared-memory row strides */) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16 *sq = reinterpret_cast<bf16 *>(smem_raw);              // [32][k_stride]
-    bf16 *sk0 = sq + kGRows * k_stride;                         // [2][32][k_stride]
-    bf16 *sv0 = sk0 + 2 * kGKeys * k_stride;                    // [2][32][v_stride]
-    bf16 *sp = sv0 + 2 * kGKeys * v_stride;                     // [32][kGSP]
+    bf16 *skv = sq + kGRows * k_stride;                         // [2] x ([32][k_stride] keys | [32][v_stride] values)
+    const int buf_elems = kGKeys * (k_stride + v_stride);
+    bf16 *sp = skv + 2 * buf_elems;                             // [32][kGSP]
     float *ss = reinterpret_cast<float *>(sp + kGRows * kGSP);  // [32][kGSS]
     float *s_alpha = ss + kGRows * kGSS;                        // [32]
     float *s_l = s_alpha + kGRows;                              // [32]
@@ -79,7 +80,7 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
     const int k_pieces = dk / 8, v_pieces = dv / 8;  // 16-byte pieces of a key / value row
 
     // zero everything once: padding columns of Q, K and V must read as zero in every product
-    for (int i = threadIdx.x; i < ((kGRows + 2 * kGKeys) * k_stride + 2 * kGKeys * v_stride) / 8; i += blockDim.x)
+    for (int i = threadIdx.x; i < (kGRows * k_stride + 2 * buf_elems) / 8; i += blockDim.x)
         reinterpret_cast<uint4 *>(sq)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
     for (int r = warp; r < kGRows; r += kGWarps) {  // row = token-in-tile * hp + head-in-group
@@ -98,34 +99,40 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
     const int n_tiles = (hi - lo) / kGKeys + 1;
     const size_t k_off = (size_t)g * dk, v_off = (size_t)kv_heads * dk + (size_t)g * dv;
 
+    // which 16-byte piece of which row this thread copies first (the same for every tile); the next ones are 256 pieces on
+    const int per_row = k_pieces + v_pieces;
+    const int step_rows = (int)blockDim.x / per_row, step_pieces = (int)blockDim.x % per_row;
     auto stage = [&](int tile, int buf) {
-        bf16 *sk = sk0 + buf * kGKeys * k_stride, *sv = sv0 + buf * kGKeys * v_stride;
+        bf16 *sk = skv + buf * buf_elems, *sv = sk + kGKeys * k_stride;
         int k0 = lo + tile * kGKeys;
         int page = table[k0 / page_size];
         bool ok = page >= 0 && page < num_pages;
         int valid = ok ? min(kGKeys, hi - k0 + 1) : 0;
         const bf16 *src = slab + ((size_t)(ok ? page : 0) * page_size + (k0 % page_size)) * row_width;
-        const int per_row = k_pieces + v_pieces;
-        for (int idx = threadIdx.x; idx < kGKeys * per_row; idx += blockDim.x) {  // one 16-byte piece of a key or value row each
-            int j = idx / per_row, piece = idx - j * per_row;
+        int j = (int)threadIdx.x / per_row, piece = (int)threadIdx.x % per_row;
+        while (j < kGKeys) {
             bool is_v = piece >= k_pieces;
             int col = (is_v ? piece - k_pieces : piece) * 8;
             bf16 *dst = is_v ? sv + j * v_stride + col : sk + j * k_stride + col;
             if (j < valid) g_cp16(dst, src + (size_t)j * row_width + (is_v ? v_off : k_off) + col);
             else *reinterpret_cast<uint4 *>(dst) = make_uint4(0, 0, 0, 0);
+            j += step_rows, piece += step_pieces;
+            if (piece >= per_row) piece -= per_row, ++j;
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
     // softmax state of the row this lane works on (a warp owns 4 rows, 8 lanes each; uniform over the 8 lanes)
     float m_row = sink ? 0.f : -INFINITY, l_row = sink ? 1.f : 0.f;
-    int pos_row;
-    bool live_row;
+    int see_lo = 1, see_hi = 0;  // the keys this row may see (none for a padding row)
     {
         int r = warp * 4 + (lane >> 3), tq = r / hp, hh = r % hp;
-        live_row = tq < count && hh < nheads;
-        pos_row = pos0 + tq;
+        if (tq < count && hh < nheads) {
+            see_hi = pos0 + tq;
+            see_lo = mask == 1 ? max(0, see_hi - mask_size + 1) : mask == 2 ? see_hi / mask_size * mask_size : 0;
+        }
     }
+    const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
     const int mt = warp & 1, nt = warp >> 1;  // score block of this warp; nt is also its quarter of the value columns
     float acc[2 * PAIRS][4];
 #pragma unroll
@@ -136,7 +143,7 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
     stage(0, 0);
     for (int tile = 0; tile < n_tiles; ++tile) {
         const int buf = tile & 1;
-        const bf16 *sk = sk0 + buf * kGKeys * k_stride, *sv = sv0 + buf * kGKeys * v_stride;
+        const bf16 *sk = skv + buf * buf_elems, *sv = sk + kGKeys * k_stride;
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();  // this tile has landed, and every warp is done with the previous one: its buffer may be refilled
         if (tile + 1 < n_tiles) stage(tile + 1, buf ^ 1);
@@ -177,9 +184,9 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
 #pragma unroll
             for (int j = 0; j < kGKeys / 8; ++j) {
                 int key = key0 + 8 * j;
-                bool vis = live_row && key <= hi && g_visible(pos_row, key, mask, mask_size);
+                bool vis = key >= see_lo && key <= see_hi;
                 float s = ss[r * kGSS + lq + 8 * j];
-                if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+                if (softcap > 0.f) s = softcap * g_tanh(s * inv_cap);
                 sv4[j] = vis ? s : -INFINITY;
                 mx = fmaxf(mx, sv4[j]);
             }
