@@ -72,8 +72,16 @@ class RaggedDecoderModel:
             state["slabs"] = self._storage_version()  # the append may have grown the pool: read it after the plan
             torch.cuda.current_stream(self.device).synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                state["logits"] = self._forward_plan(plan)
+            # The library's GEMM workspace is cached per stream, and all captures share one side stream: a workspace that was
+            # allocated inside an earlier capture lives in THAT graph's memory pool and dangles once that graph is gone.
+            # Dropping the cached workspaces around the capture keeps each graph's workspace its own.
+            drop_workspaces = getattr(torch._C, "_cuda_clearCublasWorkspaces", lambda: None)
+            drop_workspaces()
+            try:
+                with torch.cuda.graph(graph):
+                    state["logits"] = self._forward_plan(plan)
+            finally:
+                drop_workspaces()
             state["graph"], state["plan"] = graph, plan
             self.graph_captures += 1
         else:
