@@ -3,7 +3,7 @@ parameters: what a position sees (``mask`` = ``"causal"``, ``"window"``: itself 
 before it, ``"chunk"``: the earlier positions of its own block of ``mask_size`` positions counted from 0), a tanh
 ``softcap`` on the scaled scores, a ``sink`` (one more term ``exp(0)`` in the softmax's denominator), per-head RMS
 norms of queries and keys (plain weights of size ``dim``, shared by the heads) and a sigmoid output gate per head.
-Positions do not enter the scores (no rotation).
+The scores carry no positional term (nothing is rotated).
 
 The layer's input projections are made by the caller in one product (``FusedProjection``); the module takes the views
 ``q [T, H * dim]``, ``k [T, G * dim]``, ``v [T, G * vdim]`` and ``gate [T, H]`` (logits), stores keys and values in the
