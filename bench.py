@@ -1064,7 +1064,7 @@ def _bapovik_kernels(cfg: dict, device, prompt: int, batch: int, context: int) -
         gate = torch.randn((T, H), dtype=torch.float32, device=device).to(bf)
         o = torch.empty((T, H, dv), dtype=bf, device=device)
         return timed(lambda: blocks.paged_attention(q, slab, table, tiles, pos, kv_heads=G, dv=dv, mask=blocks.MASK_WINDOW, mask_size=window, scale=0.05,
-                                                    softcap=30.0, sink=True, gate=gate, out=o, kernel=kernel))
+                                                    softcap=30.0, sink=True, gate=gate, out=o, kernel=kernel, max_context=ctx))
 
     ms = attention(prompt, 1, prompt)
     seen = sum(min(i + 1, window) for i in range(prompt))

@@ -114,7 +114,11 @@ int tlb_paged_attention_mma_supported(int dk, int dv, int kv_heads, int page_siz
 int tlb_paged_attention_mma(const void *q, long long q_token, long long q_head, const void *slab, int num_pages, int page_size, int dk, int dv,
                             int heads, int kv_heads, const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles,
                             const int32_t *tok_pos, int mask, int mask_size, float scale, float softcap, int sink, const void *gate,
-                            long long g_token, void *out, long long o_token, long long o_head, void *stream);
+                            long long g_token, void *out, long long o_token, long long o_head, int splits, void *workspace,
+                            size_t workspace_bytes, void *stream);
+/* splits > 1 cuts every tile's key range over that many CTAs (few query rows, long key ranges) and a second launch merges the
+ * partial sums; workspace: tlb_paged_attention_mma_workspace(...) bytes, no initialisation needed. */
+size_t tlb_paged_attention_mma_workspace(int num_tiles, int heads, int kv_heads, int dv, int splits);
 /* Before that attention: per-head RMS norm (plain weight [dk]) of the queries in place (q_norm != NULL) and of the keys
  * (k_norm != NULL), and the token's keys and values stored at its slot of the cache (k != NULL). */
 int tlb_kv_prepare(void *q, long long q_token, long long q_head, int heads, const void *q_norm, const void *k, long long k_token, long long k_head,

@@ -135,6 +135,29 @@ def test_tensor_core_attention_against_plain_attention_and_the_general_kernel(de
     assert blocks.paged_attention_kernel(bf, 4, 2, 12, 16, 32)[0] == "general" and blocks.paged_attention_kernel(torch.float32, 4, 2, 16, 16, 32)[0] == "general"
 
 
+@pytest.mark.parametrize("kind,size,sink", [("causal", 0, True), ("window", 300, False), ("chunk", 512, True), ("window", 40, True)])
+def test_split_key_range_merges_to_the_same_rows(dev, kind, size, sink):
+    """A few single tokens over a long key range: the tensor-core kernel cuts the range over several CTAs and merges
+    (the sink counted once, splits without a visible key weigh nothing); against the plain rows and the unsplit launch."""
+    g = torch.Generator().manual_seed(size)
+    S, heads, kv_heads, dk, dv, bf = 700, 4, 2, 32, 48, torch.bfloat16
+    q, k, v = torch.randn(S, heads, dk, generator=g).to(bf), torch.randn(S, kv_heads, dk, generator=g).to(bf), torch.randn(S, kv_heads, dv, generator=g).to(bf)
+    gate = torch.randn(S, heads, generator=g).to(bf)
+    want = O.masked_attention(q.double(), k.double(), v.double(), scale=dk ** -0.5, kind=kind, size=size, softcap=5.0, sink=sink)
+    want = want * torch.sigmoid(gate.double())[:, :, None]
+    cache = Paged(dev, bf, k, v)
+    name, tile = blocks.paged_attention_kernel(bf, heads, kv_heads, dk, dv, 32)
+    args = dict(kv_heads=kv_heads, dv=dv, mask=MASK[kind], mask_size=size, scale=dk ** -0.5, softcap=5.0, sink=sink, kernel=name)
+    for i in (S - 1, 640, 511, 512):
+        tiles, pos = cache.tiles(dev, i, 1, tile)
+        split = blocks.paged_attention(q[i : i + 1].to(dev), cache.slab, cache.table, tiles, pos, gate=gate[i : i + 1].to(dev), max_context=i + 1, **args)
+        whole = blocks.paged_attention(q[i : i + 1].to(dev), cache.slab, cache.table, tiles, pos, gate=gate[i : i + 1].to(dev), **args)
+        close(split, want[i : i + 1], 2e-2)
+        close(split, whole.double().cpu(), 1e-2)
+    reach = S if kind == "causal" else min(S, size)
+    assert blocks.attention_splits(2, reach, dev) == max(1, min(32, reach // 128))
+
+
 @pytest.mark.parametrize("kernel", ["general", "mma"])
 @pytest.mark.parametrize("kind,size", [("window", 70), ("window", 64), ("chunk", 70), ("chunk", 64), ("causal", 0)])
 def test_one_key_that_matters_far_away_at_page_borders_and_mask_edges(dev, kind, size, kernel):

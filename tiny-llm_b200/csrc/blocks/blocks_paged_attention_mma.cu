@@ -12,7 +12,9 @@
 //               what a row sees is a key range worked out once per row, the cap's tanh is the hardware approximation;
 //   3. values:  O[32 x dv] += P V, warp = (16-row half, quarter of the value columns).
 // A row's arithmetic depends only on its own position (32-aligned key tiles in ascending order): what else is in the
-// CTA, the launch or the batch does not change its result, nor does where a prompt was cut.
+// CTA, the launch or the batch does not change its result, nor does where a prompt was cut.  When a launch alone would
+// leave most SMs idle (a few single tokens over long key ranges), the caller may cut every tile's key range over several
+// CTAs (flash decoding): partial sums go to a workspace and a second launch merges them; that changes rounding only.
 #include "blocks_common.cuh"
 
 namespace tlb {
@@ -59,7 +61,8 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
                            int row_width, int dk, int dv, int heads, int kv_heads, int hp /* query heads per CTA */,
                            const int32_t *__restrict__ block_table, int max_pages, const int32_t *__restrict__ tiles, const int32_t *__restrict__ tok_pos,
                            int mask, int mask_size, float scale, float softcap, int sink, const bf16 *__restrict__ gate, long long g_token,
-                           bf16 *__restrict__ out, long long o_token, long long o_head, int k_stride, int v_stride /* shared-memory row strides */) {
+                           bf16 *__restrict__ out, long long o_token, long long o_head, int k_stride, int v_stride /* shared-memory row strides */,
+                           float *__restrict__ partial /* split results, or NULL */) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16 *sq = reinterpret_cast<bf16 *>(smem_raw);              // [32][k_stride]
     bf16 *skv = sq + kGRows * k_stride;                         // [2] x ([32][k_stride] keys | [32][v_stride] values)
@@ -123,7 +126,8 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
     };
 
     // softmax state of the row this lane works on (a warp owns 4 rows, 8 lanes each; uniform over the 8 lanes)
-    float m_row = sink ? 0.f : -INFINITY, l_row = sink ? 1.f : 0.f;
+    const bool sunk = sink && blockIdx.z == 0;  // with the key range split over gridDim.z CTAs the sink's term is counted once
+    float m_row = sunk ? 0.f : -INFINITY, l_row = sunk ? 1.f : 0.f;
     int see_lo = 1, see_hi = 0;  // the keys this row may see (none for a padding row)
     {
         int r = warp * 4 + (lane >> 3), tq = r / hp, hh = r % hp;
@@ -139,14 +143,17 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
     for (int i = 0; i < 2 * PAIRS; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
     const int ksteps = (dk + 15) / 16;
+    // with the key range split over gridDim.z CTAs, this one takes a contiguous run of key tiles
+    const int per_split = (n_tiles + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int tile_begin = (int)blockIdx.z * per_split, tile_end = min(n_tiles, tile_begin + per_split);
     __syncthreads();  // the zero fill is done before the first copies land
-    stage(0, 0);
-    for (int tile = 0; tile < n_tiles; ++tile) {
-        const int buf = tile & 1;
+    if (tile_begin < tile_end) stage(tile_begin, 0);
+    for (int tile = tile_begin; tile < tile_end; ++tile) {
+        const int buf = (tile - tile_begin) & 1;
         const bf16 *sk = skv + buf * buf_elems, *sv = sk + kGKeys * k_stride;
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();  // this tile has landed, and every warp is done with the previous one: its buffer may be refilled
-        if (tile + 1 < n_tiles) stage(tile + 1, buf ^ 1);
+        if (tile + 1 < tile_end) stage(tile + 1, buf ^ 1);
 
         // 1. scores: this warp's 16 rows x 8 keys
         {
@@ -232,8 +239,25 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
     }
 
     __syncthreads();  // the last tile's rescale factors have been read
-    if ((lane & 7) == 0) s_l[warp * 4 + (lane >> 3)] = l_row;
+    if ((lane & 7) == 0) s_l[warp * 4 + (lane >> 3)] = l_row, s_alpha[warp * 4 + (lane >> 3)] = m_row;
     __syncthreads();
+    if (partial != nullptr) {
+        // split results: [cta (x, y)][split][32 rows][value columns + 2] fp32: un-normalised sums, then the maximum and the sum
+        const int cols = 64 * PAIRS + 2;
+        float *dst = partial + (((size_t)blockIdx.y * gridDim.x + blockIdx.x) * gridDim.z + blockIdx.z) * kGRows * cols;
+        int gq = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            int r = mt * 16 + gq + half * 8;
+#pragma unroll
+            for (int i = 0; i < 2 * PAIRS; ++i) {
+                int col = nt * (16 * PAIRS) + i * 8 + 2 * t;
+                dst[r * cols + col] = acc[i][half * 2], dst[r * cols + col + 1] = acc[i][half * 2 + 1];
+            }
+        }
+        if (threadIdx.x < kGRows) dst[threadIdx.x * cols + 64 * PAIRS] = s_alpha[threadIdx.x], dst[threadIdx.x * cols + 64 * PAIRS + 1] = s_l[threadIdx.x];
+        return;
+    }
     {
         int gq = lane >> 2, t = lane & 3;
 #pragma unroll
@@ -251,6 +275,47 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
                 if (col + 1 < dv) o[col + 1] = __float2bfloat16_rn(acc[i][half * 2 + 1] * inv);
             }
         }
+    }
+}
+
+// Combine the split results of one query row per CTA: weights exp(m_z - max m), added in split order; then the gate.
+__global__ void __launch_bounds__(128)
+paged_attention_merge_kernel(const float *__restrict__ part, int splits, int cols, const int32_t *__restrict__ tiles, int heads, int kv_heads, int hp,
+                             int dv, const bf16 *__restrict__ gate, long long g_token, bf16 *__restrict__ out, long long o_token, long long o_head) {
+    __shared__ float weight[64];
+    __shared__ float inv_l;
+    const int group = heads / kv_heads, parts = (group + hp - 1) / hp;
+    const int g = blockIdx.y / parts, piece = blockIdx.y % parts;
+    const int head0 = g * group + piece * hp, nheads = min(hp, group - piece * hp);
+    const int first = tiles[blockIdx.x * 3 + 0], count = tiles[blockIdx.x * 3 + 1];
+    const int r = blockIdx.z, tq = r / hp, hh = r % hp;
+    if (tq >= count || hh >= nheads) return;
+    const float *base = part + (((size_t)blockIdx.y * gridDim.x + blockIdx.x) * splits * kGRows + r) * cols;
+    const size_t step = (size_t)kGRows * cols;  // from one split's row to the next split's
+    if (threadIdx.x < 32) {
+        float m = -INFINITY;
+        for (int z = threadIdx.x; z < splits; z += 32) m = fmaxf(m, base[z * step + cols - 2]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int z = threadIdx.x; z < splits; z += 32) {
+            float mz = base[z * step + cols - 2];
+            float w = mz == -INFINITY ? 0.f : expf(mz - m);
+            weight[z] = w;
+            l += base[z * step + cols - 1] * w;
+        }
+        l = warp_sum(l);
+        if (threadIdx.x == 0) {
+            float inv = 1.0f / l;
+            if (gate) inv *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)(first + tq) * g_token + head0 + hh])));
+            inv_l = inv;
+        }
+    }
+    __syncthreads();
+    bf16 *o = out + (size_t)(first + tq) * o_token + (size_t)(head0 + hh) * o_head;
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+        float v = 0.f;
+        for (int z = 0; z < splits; ++z) v = fmaf(base[z * step + c], weight[z], v);
+        o[c] = __float2bfloat16_rn(v * inv_l);
     }
 }
 
@@ -276,10 +341,17 @@ int tlb_paged_attention_mma_supported(int dk, int dv, int kv_heads, int page_siz
     return dk > 0 && dv > 0 && dk % 8 == 0 && dv % 8 == 0 && dk <= 256 && dv <= 256 && kv_heads > 0 && page_size % kGKeys == 0;
 }
 
+// Bytes of workspace for `splits` > 1 (0 for one split).
+size_t tlb_paged_attention_mma_workspace(int num_tiles, int heads, int kv_heads, int dv, int splits) {
+    if (splits <= 1 || heads <= 0 || kv_heads <= 0 || heads % kv_heads) return 0;
+    int group = heads / kv_heads, hp = group >= kGRows ? kGRows : group;
+    return (size_t)num_tiles * kv_heads * ceil_div(group, hp) * splits * kGRows * (64 * g_pairs(dv) + 2) * sizeof(float);
+}
+
 int tlb_paged_attention_mma(const void *q, long long q_token, long long q_head, const void *slab, int num_pages, int page_size, int dk, int dv, int heads,
                             int kv_heads, const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles, const int32_t *tok_pos,
                             int mask, int mask_size, float scale, float softcap, int sink, const void *gate, long long g_token, void *out,
-                            long long o_token, long long o_head, void *stream) {
+                            long long o_token, long long o_head, int splits, void *workspace, size_t workspace_bytes, void *stream) {
     if (num_tiles <= 0) return TL_OK;
     if (!q || !slab || !block_table || !tiles || !tok_pos || !out || heads <= 0 || kv_heads <= 0 || heads % kv_heads || max_pages <= 0 || num_pages <= 0)
         return tl::fail(TL_EINVAL, "paged_attention_mma: bad argument");
@@ -290,10 +362,15 @@ int tlb_paged_attention_mma(const void *q, long long q_token, long long q_head, 
     int group = heads / kv_heads;
     int hp = group >= kGRows ? kGRows : group;
     int pairs = g_pairs(dv);
+    if (splits < 1) splits = 1;
+    if (splits > 64) splits = 64;
+    if (splits > 1 && (!workspace || workspace_bytes < tlb_paged_attention_mma_workspace(num_tiles, heads, kv_heads, dv, splits)))
+        return tl::fail(TL_EWORKSPACE, "paged_attention_mma: workspace missing or too small for %d splits", splits);
+    float *part = splits > 1 ? (float *)workspace : nullptr;
     int k_stride = ceil_div(dk, 16) * 16 + 8;  // (stride / 8) odd: conflict-free ldmatrix rows
     int v_stride = 64 * pairs + 8;
     size_t smem = (size_t)((kGRows + 2 * kGKeys) * k_stride + 2 * kGKeys * v_stride) * 2 + kGRows * kGSP * 2 + (size_t)kGRows * kGSS * 4 + 2 * kGRows * 4;
-    dim3 grid(num_tiles, kv_heads * ceil_div(group, hp));
+    dim3 grid(num_tiles, kv_heads * ceil_div(group, hp), splits);
     cudaStream_t st = as_stream(stream);
 #define TLB_PAM(P)                                                                                                                               \
     do {                                                                                                                                         \
@@ -304,13 +381,18 @@ int tlb_paged_attention_mma(const void *q, long long q_token, long long q_head, 
         }                                                                                                                                        \
         kernel<<<grid, kGWarps * 32, smem, st>>>((const bf16 *)q, q_token, q_head, (const bf16 *)slab, num_pages, page_size, kv_heads * (dk + dv), dk, dv, \
                                                  heads, kv_heads, hp, block_table, max_pages, tiles, tok_pos, mask, mask_size, scale, softcap, sink,    \
-                                                 (const bf16 *)gate, g_token, (bf16 *)out, o_token, o_head, k_stride, v_stride);                        \
+                                                 (const bf16 *)gate, g_token, (bf16 *)out, o_token, o_head, k_stride, v_stride, part);                  \
     } while (0)
     if (pairs == 1) TLB_PAM(1);
     else if (pairs == 2) TLB_PAM(2);
     else TLB_PAM(4);
 #undef TLB_PAM
     TL_LAUNCH_CHECK("paged_attention_mma");
+    if (splits > 1) {
+        paged_attention_merge_kernel<<<dim3(num_tiles, kv_heads * ceil_div(group, hp), kGRows), 128, 0, st>>>(
+            part, splits, 64 * pairs + 2, tiles, heads, kv_heads, hp, dv, (const bf16 *)gate, g_token, (bf16 *)out, o_token, o_head);
+        TL_LAUNCH_CHECK("paged_attention_merge");
+    }
     return TL_OK;
 }
 

@@ -45,7 +45,9 @@ _SIGNATURES = {
     "tlb_paged_attention": (_I, [_VP, _LL, _LL, _VP, _I, _I, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _F, _I, _VP, _LL, _VP, _LL, _LL, _I, _VP]),
     "tlb_paged_attention_mma_tile_tokens": (_I, [_I, _I]),
     "tlb_paged_attention_mma_supported": (_I, [_I, _I, _I, _I]),
-    "tlb_paged_attention_mma": (_I, [_VP, _LL, _LL, _VP, _I, _I, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _F, _I, _VP, _LL, _VP, _LL, _LL, _VP]),
+    "tlb_paged_attention_mma": (_I, [_VP, _LL, _LL, _VP, _I, _I, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _F, _I, _VP, _LL, _VP, _LL, _LL, _I, _VP,
+                                     ctypes.c_size_t, _VP]),
+    "tlb_paged_attention_mma_workspace": (ctypes.c_size_t, [_I, _I, _I, _I, _I]),
     "tlb_kv_prepare": (_I, [_VP, _LL, _LL, _I, _VP, _VP, _LL, _LL, _VP, _LL, _LL, _I, _I, _I, _VP, _F, _VP, _VP, _VP, _I, _I, _I, _VP, _I, _I, _VP]),
     "tlb_decay_scan_workspace": (ctypes.c_size_t, [_I, _I, _I, _I, _I]),
     "tlb_decay_scan": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _VP, _F, _F, _I, _I, _I, _VP, _I, _I, _VP, _LL, _I, _VP, _VP, ctypes.c_size_t,
@@ -422,10 +424,12 @@ def kv_prepare(q, k, v, *, q_norm=None, k_norm=None, eps: float = 0.0, tok_pos=N
 
 
 def paged_attention(q, slab, block_table, tiles, tok_pos, *, kv_heads: int, dv: int, mask: int, mask_size: int, scale: float, softcap: float = 0.0,
-                    sink: bool = False, gate=None, out=None, kernel: str = "general"):
+                    sink: bool = False, gate=None, out=None, kernel: str = "general", max_context: int = 0):
     """``q [T, H, dk]`` (a view with unit inner stride) against ``slab [P, page, kv_heads * (dk + dv)]`` -> ``out [T, H, dv]``
     (contiguous, the query's dtype).  ``gate [T, H]`` (a view with unit inner stride): logits of a sigmoid output gate.
-    ``kernel`` and the tile size of ``tiles`` come from ``paged_attention_kernel``."""
+    ``kernel`` and the tile size of ``tiles`` come from ``paged_attention_kernel``.  ``max_context`` (the longest sequence of
+    the step, 0 = unknown) lets the tensor-core kernel split the key range over several CTAs when the launch alone would
+    leave SMs idle."""
     _gpu("paged_attention", q, slab, block_table, tiles, tok_pos, gate, out)
     _contig("paged_attention", slab, block_table, tiles, tok_pos)
     T, H, dk = q.shape
@@ -439,10 +443,18 @@ def paged_attention(q, slab, block_table, tiles, tok_pos, *, kv_heads: int, dv: 
     if kernel == "mma":
         if slab.dtype != torch.bfloat16:
             raise RuntimeError("paged_attention: the tensor-core kernel takes a bfloat16 cache")
-        _check(library().tlb_paged_attention_mma(_ptr(q), q.stride(0), q.stride(1), _ptr(slab), P, page_size, dk, dv, H, kv_heads, _ptr(block_table),
-                                                 block_table.shape[1], _ptr(tiles), tiles.shape[0], _ptr(tok_pos), int(mask), int(mask_size),
-                                                 float(scale), float(softcap or 0.0), int(bool(sink)), _ptr(gate),
-                                                 gate.stride(0) if gate is not None else 0, _ptr(out), out.stride(0), out.stride(1), _stream(q)))
+        lib = library()
+        reach = min(max_context, int(mask_size)) if mask != MASK_CAUSAL else max_context  # keys a query can see at most
+        group = H // kv_heads
+        ctas = tiles.shape[0] * kv_heads * -(-group // min(group, 32))
+        splits = attention_splits(ctas, reach, slab.device) if reach else 1
+        nbytes = int(lib.tlb_paged_attention_mma_workspace(tiles.shape[0], H, kv_heads, dv, splits))
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=slab.device) if nbytes else None
+        _check(lib.tlb_paged_attention_mma(_ptr(q), q.stride(0), q.stride(1), _ptr(slab), P, page_size, dk, dv, H, kv_heads, _ptr(block_table),
+                                           block_table.shape[1], _ptr(tiles), tiles.shape[0], _ptr(tok_pos), int(mask), int(mask_size),
+                                           float(scale), float(softcap or 0.0), int(bool(sink)), _ptr(gate),
+                                           gate.stride(0) if gate is not None else 0, _ptr(out), out.stride(0), out.stride(1), splits, _ptr(ws), nbytes,
+                                           _stream(q)))
         return out
     if kernel != "general":
         raise RuntimeError(f"paged_attention: unknown kernel {kernel!r}")

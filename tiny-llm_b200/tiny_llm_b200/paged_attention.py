@@ -79,5 +79,6 @@ class PagedGroupedAttention:
         elif self.q_norm is not None:
             blocks.kv_prepare(q3, None, None, q_norm=self.q_norm, eps=self.eps)
         o = blocks.paged_attention(q3, slab, plan.block_table, plan.tiles_for(self.tile_tokens), plan.tok_pos, kv_heads=G, dv=self.vdim, mask=self.mask,
-                                   mask_size=self.mask_size, scale=self.scale, softcap=self.softcap, sink=self.sink, gate=gate, kernel=self.kernel)
+                                   mask_size=self.mask_size, scale=self.scale, softcap=self.softcap, sink=self.sink, gate=gate, kernel=self.kernel,
+                                   max_context=getattr(plan, "max_context", 0))
         return linear_wide(o.view(T, H * self.vdim), self.w_o)  # fp32: a norm or the residual sum reads it unrounded
